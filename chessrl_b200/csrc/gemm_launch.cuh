@@ -1,0 +1,109 @@
+// Host side of the tcgen05 GEMM: tensor-map encoding (driver entry point fetched at run time, so the
+// library links against the CUDA runtime only) and tile-shape selection.
+#pragma once
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include "gemm.cuh"
+
+namespace crl {
+
+enum HostErr : int {
+  kOk = 0,
+  kErrInvalid = -1,      // bad argument (null pointer, negative size, unknown enum)
+  kErrShape = -2,        // shape or alignment the kernels cannot take
+  kErrCuda = -3,         // a CUDA runtime / driver call failed
+  kErrMissingWeight = -4,
+  kErrNotFinalized = -5,
+  kErrDeviceTimeout = -6,  // a bounded device-side wait ran out (status word holds the code)
+  kErrWorkspace = -7,
+  kErrUnsupported = -8,
+};
+
+inline PFN_cuTensorMapEncodeTiled_v12000 tmap_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [outer, inner] with a row pitch in bytes; box = 128 bytes x box_outer rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+inline int make_tmap_2d(CUtensorMap* out, const void* ptr, int esz, uint64_t inner, uint64_t outer,
+                        uint64_t pitch_bytes, uint32_t box_outer) {
+  auto enc = tmap_encoder();
+  if (enc == nullptr) return kErrCuda;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (pitch_bytes & 15) != 0) return kErrShape;
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstride[1] = {pitch_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                   const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kErrCuda;
+}
+
+struct GemmArgs {
+  int kind = kKindF16;          // MmaKind: element type of A and W
+  const void* A = nullptr;      // [M, lda]
+  long long lda = 0;            // elements
+  const void* W = nullptr;      // [N, ldw]
+  long long ldw = 0;
+  GemmParams p{};
+};
+
+template <int BN, int KIND>
+inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, KIND>;
+  static bool attr_set[64] = {};  // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
+      return kErrCuda;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, a.A, Cfg::ESZ, a.p.K, a.p.M, a.lda * Cfg::ESZ, Cfg::BM);
+  if (rc != kOk) return rc;
+  rc = make_tmap_2d(&tmB, a.W, Cfg::ESZ, a.p.K, a.p.N, a.ldw * Cfg::ESZ, BN);
+  if (rc != kOk) return rc;
+  const int tiles = ((a.p.M + Cfg::BM - 1) / Cfg::BM) * ((a.p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  gemm_tn_kernel<BN, KIND><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, a.p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+template <int KIND>
+inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
+  const int tiles_m = (a.p.M + 127) / 128;
+  int bn = 256;
+  if (a.p.N <= 64) bn = 64;
+  else if (a.p.N <= 128) bn = 128;
+  else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
+  if (bn == 64) return gemm_launch_t<64, KIND>(a, num_sms, stream);
+  if (bn == 128) return gemm_launch_t<128, KIND>(a, num_sms, stream);
+  return gemm_launch_t<256, KIND>(a, num_sms, stream);
+}
+
+inline int gemm_launch(const GemmArgs& a, int num_sms, cudaStream_t stream) {
+  if (a.A == nullptr || a.W == nullptr || a.p.C == nullptr || a.p.status == nullptr) return kErrInvalid;
+  if (a.p.M <= 0 || a.p.N <= 0 || a.p.K <= 0) return kErrInvalid;
+  switch (a.kind) {
+    case kKindF16: return gemm_launch_k<kKindF16>(a, num_sms, stream);
+    case kKindF8: return gemm_launch_k<kKindF8>(a, num_sms, stream);
+    case kKindI8: return gemm_launch_k<kKindI8>(a, num_sms, stream);
+    default: return kErrInvalid;
+  }
+}
+
+}  // namespace crl
