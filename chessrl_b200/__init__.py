@@ -1,0 +1,9 @@
+"""chessrl_b200: B200-native forward pass of the ChessRL board transformer (hand-written sm_100a CUDA
+behind a C ABI, see include/chessrl_b200.h)."""
+from ._lib import (CrlError, LN_POST, LN_PRE, ACT_GELU, ACT_MISH, FFN_ACT_END, FFN_ACT_MID, BIAS_NONE, BIAS_CAUSAL,
+                   BIAS_RELPOS, BIAS_SMOLGEN, POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858, VALUE_NONE, VALUE_WDL,
+                   VALUE_WDL_Q, DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8, MASK_NONE, MASK_BITS, MASK_ADDITIVE)
+from .engine import Engine, EngineConfig
+from .modules import BoardTransformer, BT4, BT4Planes19, BT4Baseline
+
+__all__ = ["Engine", "EngineConfig", "BoardTransformer", "BT4", "BT4Planes19", "BT4Baseline", "CrlError"]

@@ -1,0 +1,110 @@
+"""ctypes binding of libchessrl_b200.so (the C ABI in include/chessrl_b200.h).
+
+There is no CPU fallback: if the library is missing this module raises at import of the symbols, and
+every compute entry point needs a B200.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libchessrl_b200.so")
+
+# enums of include/chessrl_b200.h
+LN_POST, LN_PRE = 0, 1
+ACT_GELU, ACT_MISH = 1, 2
+FFN_ACT_END, FFN_ACT_MID = 0, 1
+BIAS_NONE, BIAS_CAUSAL, BIAS_RELPOS, BIAS_SMOLGEN = 0, 1, 2, 3
+POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858 = 0, 1, 2
+VALUE_NONE, VALUE_WDL, VALUE_WDL_Q = 0, 1, 2
+DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8 = 0, 1, 2
+LAYOUT_NHWC_F32, LAYOUT_NHWC_F16, LAYOUT_NCHW_F16, LAYOUT_NCHW_F32 = 0, 1, 2, 3
+MASK_NONE, MASK_BITS, MASK_ADDITIVE = 0, 1, 2
+OUT_F32, OUT_F16 = 0, 1
+
+EXPORTS = [
+    "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
+    "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
+    "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
+    "crl_vocab_mirror_index",
+]
+
+
+class Config(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "planes", "d_model", "n_layers", "n_heads", "d_ff", "ln_mode", "act", "ffn_act_pos", "bias_mode",
+        "policy_mode", "value_mode", "dtype", "smolgen_compress", "smolgen_hidden", "smolgen_gen", "chunk")]
+
+
+class IO(ctypes.Structure):
+    _fields_ = [
+        ("planes", ctypes.c_void_p), ("layout", ctypes.c_int32), ("batch", ctypes.c_int64),
+        ("legal_mask", ctypes.c_void_p), ("mask_mode", ctypes.c_int32), ("mask_stride", ctypes.c_int64),
+        ("policy_out", ctypes.c_void_p), ("policy_dtype", ctypes.c_int32), ("policy_softmax", ctypes.c_int32),
+        ("policy_stride", ctypes.c_int64),
+        ("wdl_out", ctypes.c_void_p), ("wdl_softmax", ctypes.c_int32),
+        ("q_out", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library (once) and declare the signatures. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m chessrl_b200.build` (needs nvcc). "
+            "chessrl_b200 has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.crl_create.argtypes = [ctypes.POINTER(Config), ctypes.c_int, ctypes.POINTER(vp)]
+    lib.crl_create.restype = ctypes.c_int
+    lib.crl_destroy.argtypes = [vp]
+    lib.crl_destroy.restype = None
+    lib.crl_set_weight.argtypes = [vp, ctypes.c_char_p, vp, i64]
+    lib.crl_set_weight.restype = ctypes.c_int
+    lib.crl_num_required_keys.argtypes = [vp]
+    lib.crl_num_required_keys.restype = ctypes.c_int
+    lib.crl_required_key.argtypes = [vp, ctypes.c_int]
+    lib.crl_required_key.restype = ctypes.c_char_p
+    lib.crl_finalize.argtypes = [vp]
+    lib.crl_finalize.restype = ctypes.c_int
+    lib.crl_calibrate.argtypes = [vp, vp, i32, i64, vp, ctypes.c_size_t, vp]
+    lib.crl_calibrate.restype = ctypes.c_int
+    lib.crl_workspace_bytes.argtypes = [vp, i64]
+    lib.crl_workspace_bytes.restype = ctypes.c_size_t
+    lib.crl_num_moves.argtypes = [vp]
+    lib.crl_num_moves.restype = ctypes.c_int
+    lib.crl_forward.argtypes = [vp, ctypes.POINTER(IO)]
+    lib.crl_forward.restype = ctypes.c_int
+    lib.crl_forward_host.argtypes = [vp, ctypes.POINTER(IO)]
+    lib.crl_forward_host.restype = ctypes.c_int
+    lib.crl_last_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+    lib.crl_last_status.restype = ctypes.c_int
+    lib.crl_last_launch_count.argtypes = [vp]
+    lib.crl_last_launch_count.restype = i64
+    lib.crl_error_detail.argtypes = [vp]
+    lib.crl_error_detail.restype = ctypes.c_char_p
+    lib.crl_strerror.argtypes = [ctypes.c_int]
+    lib.crl_strerror.restype = ctypes.c_char_p
+    lib.crl_linear.argtypes = [ctypes.c_int, vp, i64, vp, i64, vp, i64, ctypes.c_int, i64, i64, i64, vp, vp, i64,
+                               ctypes.c_float, ctypes.c_int, vp, vp]
+    lib.crl_linear.restype = ctypes.c_int
+    lib.crl_vocab_move.argtypes = [ctypes.c_int, ctypes.c_char_p]
+    lib.crl_vocab_move.restype = ctypes.c_int
+    lib.crl_vocab_mirror_index.argtypes = [ctypes.c_int]
+    lib.crl_vocab_mirror_index.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+class CrlError(RuntimeError):
+    def __init__(self, code, detail=""):
+        self.code = code
+        msg = load().crl_strerror(code).decode()
+        super().__init__(f"chessrl_b200 error {code} ({msg})" + (f": {detail}" if detail else ""))

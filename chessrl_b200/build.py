@@ -1,0 +1,48 @@
+"""Builds libchessrl_b200.so (hand-written sm_100a CUDA + the C ABI) in-tree with nvcc.
+
+    python -m chessrl_b200.build [--force]
+
+nvcc cross-compiles without a GPU. The library sits next to this file so that it travels with the
+source tree; nothing is installed into site-packages.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libchessrl_b200.so")
+SOURCES = ["engine.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false",
+]
+
+
+def _newest_source_mtime():
+    newest = 0.0
+    for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+        for name in os.listdir(root):
+            newest = max(newest, os.path.getmtime(os.path.join(root, name)))
+    return newest
+
+
+def build(force=False, verbose=False):
+    """Compile if the library is missing or older than any source; returns the library path."""
+    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source_mtime():
+        return LIB
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    if verbose:
+        print(proc.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -27,6 +27,7 @@ struct GemmParams {
   const float* bias;       // [N] or null
   const __half* residual;  // [M, ldr] f16 or null; added after the activation
   long long ldr;
+  int res_mod;             // > 0: residual row = row % res_mod (a table broadcast over boards)
   float alpha;             // multiplies the accumulator (per-tensor dequantisation scale)
   const float* row_scale;  // [M] or null (per-token int8 scales)
   const float* col_scale;  // [N] or null (per-output-channel int8 scales)
@@ -231,6 +232,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
+      const int rrow = p.res_mod > 0 ? row % p.res_mod : row;
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
       const float a_scale = p.alpha * rs;
 #pragma unroll 1
@@ -267,7 +269,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if (row_ok) {
             if (p.residual != nullptr) {
-              const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + (long long)row * p.ldr + c0);
+              const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + (long long)rrow * p.ldr + c0);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const uint4 u = r4[q];
@@ -300,7 +302,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (p.col_scale != nullptr) x *= p.col_scale[col];
               if (p.bias != nullptr) x += p.bias[col];
               x = apply_act(x, p.act);
-              if (p.residual != nullptr) x += __half2float(p.residual[(long long)row * p.ldr + col]);
+              if (p.residual != nullptr) x += __half2float(p.residual[(long long)rrow * p.ldr + col]);
               if (p.out_dtype == kOutE4M3) x *= p.out_scale;
               store_one(p.C, p.out_dtype, (long long)row * p.ldc + col, x);
             }

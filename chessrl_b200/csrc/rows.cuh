@@ -1,0 +1,223 @@
+// Memory-bound row kernels around the GEMMs: input-plane conversion, LayerNorm (+ the embedding's
+// gating, + an optional e4m3 copy for the next FP8 GEMM), the value-head tail, and absolute-maximum
+// reduction used for FP8 calibration. All are vectorised to 16-byte accesses along the row.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "ptx.cuh"
+
+namespace crl {
+
+enum PlaneLayout : int {
+  kLayoutNHWC_F32 = 0,   // [B, 8, 8, P] f32 - the nn.Module signature (value_q.py:156-159)
+  kLayoutNHWC_F16 = 1,   // [B, 8, 8, P] f16
+  kLayoutNCHW_F16 = 2,   // [B, P, 8, 8] f16 - what the Leela server feeds (Leela/server.py:54)
+  kLayoutNCHW_F32 = 3,   // [B, P, 8, 8] f32
+};
+
+// token-major rows [B*64, ldo] f16 with zero padding in columns [P, ldo)
+template <typename TIn>
+__global__ void tokens_from_nhwc_kernel(const TIn* __restrict__ in, __half* __restrict__ out, long long rows,
+                                        int P, int ldo) {
+  const int chunks = ldo / 8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * chunks) return;
+  const long long r = i / chunks;
+  const int c0 = static_cast<int>(i % chunks) * 8;
+  __align__(16) __half h[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = c0 + j;
+    float v = 0.0f;
+    if (c < P) v = static_cast<float>(in[r * P + c]);
+    h[j] = __float2half_rn(v);
+  }
+  *reinterpret_cast<uint4*>(out + r * ldo + c0) = *reinterpret_cast<const uint4*>(h);
+}
+
+// one block per board: [P][64] -> [64][ldo] through shared memory
+template <typename TIn>
+__global__ void tokens_from_nchw_kernel(const TIn* __restrict__ in, __half* __restrict__ out, int P, int ldo) {
+  extern __shared__ __half tile[];   // [P][66]
+  const long long b = blockIdx.x;
+  const TIn* src = in + b * P * 64;
+  for (int i = threadIdx.x; i < P * 64; i += blockDim.x)
+    tile[(i >> 6) * 66 + (i & 63)] = __float2half_rn(static_cast<float>(src[i]));
+  __syncthreads();
+  __half* dst = out + b * 64 * ldo;
+  for (int i = threadIdx.x; i < 64 * ldo; i += blockDim.x) {
+    const int tok = i / ldo, c = i % ldo;
+    dst[i] = c < P ? tile[c * 66 + tok] : __float2half_rn(0.0f);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm over rows of up to 1024 f16 elements (eps 1e-5, affine), one warp per row.
+//   y = LN(x) * w + b ; optional gating y = y * ea[token] + gb[token] (token = row % 64; ea = exp(a),
+//   utils/fen_encoder.py:41-49); writes f16 and/or e4m3 (y * out8_scale).
+// ---------------------------------------------------------------------------------------------
+struct LnParams {
+  const __half* x; long long ldx;
+  long long rows; int d;
+  const float* w; const float* b;
+  const float* gate_ea; const float* gate_b;   // [64, d] or null
+  __half* y; long long ldy;                    // nullable
+  uint8_t* y8; long long ldy8; float out8_scale;  // nullable
+};
+
+__global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= p.rows) return;
+  constexpr int NV = 4;                 // up to 4 x (32 lanes x 8 elements) = 1024 columns
+  float v[NV][8];
+  const __half* xr = p.x + row * p.ldx;
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < p.d) {
+      const uint4 u = *reinterpret_cast<const uint4*>(xr + c);
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        v[i][2 * j] = f.x; v[i][2 * j + 1] = f.y;
+        sum += f.x + f.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float mean = sum / p.d;
+  float var = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < p.d) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float dlt = v[i][j] - mean; var += dlt * dlt; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+  const float rstd = rsqrtf(var / p.d + 1e-5f);
+  const int tok = static_cast<int>(row & 63);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < p.d) {
+      float y[8];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const float4 w4 = __ldg(reinterpret_cast<const float4*>(p.w + c) + q);
+        const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.b + c) + q);
+        y[q * 4 + 0] = (v[i][q * 4 + 0] - mean) * rstd * w4.x + b4.x;
+        y[q * 4 + 1] = (v[i][q * 4 + 1] - mean) * rstd * w4.y + b4.y;
+        y[q * 4 + 2] = (v[i][q * 4 + 2] - mean) * rstd * w4.z + b4.z;
+        y[q * 4 + 3] = (v[i][q * 4 + 3] - mean) * rstd * w4.w + b4.w;
+      }
+      if (p.gate_ea != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float4 e4 = __ldg(reinterpret_cast<const float4*>(p.gate_ea + (long long)tok * p.d + c) + q);
+          const float4 g4 = __ldg(reinterpret_cast<const float4*>(p.gate_b + (long long)tok * p.d + c) + q);
+          y[q * 4 + 0] = y[q * 4 + 0] * e4.x + g4.x;
+          y[q * 4 + 1] = y[q * 4 + 1] * e4.y + g4.y;
+          y[q * 4 + 2] = y[q * 4 + 2] * e4.z + g4.z;
+          y[q * 4 + 3] = y[q * 4 + 3] * e4.w + g4.w;
+        }
+      }
+      if (p.y != nullptr) {
+        uint4 pk;
+        __half2 h0 = __floats2half2_rn(y[0], y[1]), h1 = __floats2half2_rn(y[2], y[3]);
+        __half2 h2 = __floats2half2_rn(y[4], y[5]), h3 = __floats2half2_rn(y[6], y[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(p.y + row * p.ldy + c) = pk;
+      }
+      if (p.y8 != nullptr) {
+        const float s = p.out8_scale;
+        uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(y[0] * s, y[1] * s), __NV_SATFINITE, __NV_E4M3) |
+                      (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(y[2] * s, y[3] * s), __NV_SATFINITE, __NV_E4M3)) << 16);
+        uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(y[4] * s, y[5] * s), __NV_SATFINITE, __NV_E4M3) |
+                      (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(y[6] * s, y[7] * s), __NV_SATFINITE, __NV_E4M3)) << 16);
+        *reinterpret_cast<uint2*>(p.y8 + row * p.ldy8 + c) = make_uint2(lo, hi);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Value-head tail (new_paradigm/value.py:427-435 last layer + the softmax of value.py:271):
+// in [B,128] f16 -> Linear(128 -> n_out) -> mode 0 raw / 1 softmax / 2 tanh -> out [B, n_out] f32.
+// One warp per board.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) value_tail_kernel(const __half* __restrict__ in, const float* __restrict__ w,
+                                                         const float* __restrict__ b, float* __restrict__ out,
+                                                         long long B, int n_out, int mode) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= B) return;
+  const uint2 u = *reinterpret_cast<const uint2*>(in + row * 128 + lane * 4);
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+  const float2 x01 = __half22float2(h[0]), x23 = __half22float2(h[1]);
+  float acc[3] = {0.0f, 0.0f, 0.0f};
+  for (int o = 0; o < n_out && o < 3; ++o) {
+    const float4 w4 = __ldg(reinterpret_cast<const float4*>(w + o * 128 + lane * 4));
+    float s = x01.x * w4.x + x01.y * w4.y + x23.x * w4.z + x23.y * w4.w;
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+    acc[o] = s + b[o];
+  }
+  if (lane == 0) {
+    if (mode == 1) {
+      float m = acc[0];
+      for (int o = 1; o < n_out; ++o) m = fmaxf(m, acc[o]);
+      float e[3], sum = 0.0f;
+      for (int o = 0; o < n_out; ++o) { e[o] = __expf(acc[o] - m); sum += e[o]; }
+      for (int o = 0; o < n_out; ++o) out[row * n_out + o] = e[o] / sum;
+    } else if (mode == 2) {
+      for (int o = 0; o < n_out; ++o) out[row * n_out + o] = tanhf(acc[o]);
+    } else {
+      for (int o = 0; o < n_out; ++o) out[row * n_out + o] = acc[o];
+    }
+  }
+}
+
+// max |x| over an f16 buffer (grid-stride), result combined with atomicMax on the float's bit pattern
+__global__ void absmax_f16_kernel(const __half* __restrict__ x, long long rows, int cols, long long ld,
+                                  unsigned int* __restrict__ out_bits) {
+  float m = 0.0f;
+  const long long total = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int c = static_cast<int>(i % cols);
+    m = fmaxf(m, fabsf(__half2float(x[r * ld + c])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
+}
+
+// f16 -> e4m3 with a per-tensor scale (used where the producer kernel cannot emit e4m3 itself)
+__global__ void quant_e4m3_kernel(const __half* __restrict__ x, uint8_t* __restrict__ y, long long n8, float scale) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 u = reinterpret_cast<const uint4*>(x)[i];
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+  uint32_t w[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float2 a = __half22float2(h[2 * j]), b = __half22float2(h[2 * j + 1]);
+    w[j] = __nv_cvt_float2_to_fp8x2(make_float2(a.x * scale, a.y * scale), __NV_SATFINITE, __NV_E4M3) |
+           (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(b.x * scale, b.y * scale), __NV_SATFINITE, __NV_E4M3)) << 16);
+  }
+  reinterpret_cast<uint2*>(y)[i] = make_uint2(w[0], w[1]);
+}
+
+}  // namespace crl

@@ -1,0 +1,192 @@
+"""Python face of the C ABI: an `Engine` owns one `crl_handle` on one GPU and moves torch tensors in
+and out by raw pointer. torch is used for device memory and streams only; all arithmetic happens in
+libchessrl_b200.so."""
+import ctypes
+from dataclasses import dataclass, asdict
+
+import torch
+
+from . import _lib as L
+
+
+@dataclass
+class EngineConfig:
+    """Mirror of `crl_config` (include/chessrl_b200.h)."""
+    planes: int = 112
+    d_model: int = 512
+    n_layers: int = 10
+    n_heads: int = 8
+    d_ff: int = 736
+    ln_mode: int = L.LN_POST
+    act: int = L.ACT_GELU
+    ffn_act_pos: int = L.FFN_ACT_END
+    bias_mode: int = L.BIAS_RELPOS
+    policy_mode: int = L.POLICY_DENSE4096
+    value_mode: int = L.VALUE_WDL_Q
+    dtype: int = L.DTYPE_F16
+    smolgen_compress: int = 32
+    smolgen_hidden: int = 256
+    smolgen_gen: int = 256
+    chunk: int = 0
+
+    @staticmethod
+    def reference_value_q(n_layers=10, d_model=512, d_ff=736, n_heads=8, **kw):
+        """`BT4(num_layers, d_model, d_ff, num_heads)` of new_paradigm/value_q.py:122 (112 planes)."""
+        return EngineConfig(112, d_model, n_layers, n_heads, d_ff, **kw)
+
+    @staticmethod
+    def reference_value(n_layers=10, d_model=512, d_ff=736, n_heads=8, **kw):
+        """`BT4` of new_paradigm/value.py:122 (19 planes, WDL head)."""
+        return EngineConfig(19, d_model, n_layers, n_heads, d_ff, value_mode=L.VALUE_WDL, **kw)
+
+    @staticmethod
+    def baseline(n_layers, d_model, d_ff, n_heads, smolgen=True, value_only=False, **kw):
+        """Network of the target specification: post-LN, Mish between ff1 and ff2, smolgen bias, gather
+        policy over the 1858 Leela moves, WDL head."""
+        return EngineConfig(112, d_model, n_layers, n_heads, d_ff, L.LN_POST, L.ACT_MISH, L.FFN_ACT_MID,
+                            L.BIAS_SMOLGEN if smolgen else L.BIAS_NONE,
+                            L.POLICY_NONE if value_only else L.POLICY_GATHER1858, L.VALUE_WDL, **kw)
+
+    def to_c(self):
+        return L.Config(**asdict(self))
+
+
+_LAYOUT_OF = {
+    ("nhwc", torch.float32): L.LAYOUT_NHWC_F32, ("nhwc", torch.float16): L.LAYOUT_NHWC_F16,
+    ("nchw", torch.float16): L.LAYOUT_NCHW_F16, ("nchw", torch.float32): L.LAYOUT_NCHW_F32,
+}
+
+
+class Engine:
+    def __init__(self, cfg: EngineConfig, device=0):
+        self.lib = L.load()
+        self.cfg = cfg
+        self.device = torch.device("cuda", device) if not isinstance(device, torch.device) else device
+        self._h = ctypes.c_void_p()
+        c = cfg.to_c()
+        rc = self.lib.crl_create(ctypes.byref(c), self.device.index or 0, ctypes.byref(self._h))
+        if rc != 0:
+            raise L.CrlError(rc, "crl_create")
+        self._ws = None
+        self.n_moves = self.lib.crl_num_moves(self._h)
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self.lib.crl_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise L.CrlError(rc, f"{what}: {self.lib.crl_error_detail(self._h).decode()}")
+
+    # ---- weights ---------------------------------------------------------------------------------
+    def required_keys(self):
+        n = self.lib.crl_num_required_keys(self._h)
+        return [self.lib.crl_required_key(self._h, i).decode() for i in range(n)]
+
+    def load_state_dict(self, sd):
+        """Push every key the configuration needs (reference names) and repack. Extra keys in `sd`
+        are ignored, a missing one raises (CRL_ERR_MISSING_WEIGHT names it)."""
+        for k in self.required_keys():
+            if k not in sd:
+                raise L.CrlError(-4, k)
+            t = sd[k].detach().to(dtype=torch.float32).contiguous()
+            if t.is_cuda:
+                torch.cuda.synchronize(t.device)
+            self._check(self.lib.crl_set_weight(self._h, k.encode(), t.data_ptr(), t.numel()), f"set_weight {k}")
+        self._check(self.lib.crl_finalize(self._h), "finalize")
+
+    # ---- scratch ---------------------------------------------------------------------------------
+    def workspace(self, batch):
+        need = self.lib.crl_workspace_bytes(self._h, batch)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = None
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    @staticmethod
+    def _layout(planes, layout):
+        key = (layout, planes.dtype)
+        if key not in _LAYOUT_OF:
+            raise ValueError(f"unsupported planes layout/dtype {key}")
+        return _LAYOUT_OF[key]
+
+    def _batch_of(self, planes, layout):
+        p = self.cfg.planes
+        if planes.numel() % (64 * p) != 0:
+            raise ValueError("planes tensor is not a whole number of positions")
+        if layout == "nhwc" and planes.shape[-1] != p:
+            raise ValueError(f"expected {p} planes in the last dimension, got {planes.shape[-1]}")
+        return planes.numel() // (64 * p)
+
+    def calibrate(self, planes, layout="nhwc"):
+        """FP8 engines: fix the per-tensor activation scales from this batch (device tensor)."""
+        planes = planes.contiguous()
+        b = self._batch_of(planes, layout)
+        ws = self.workspace(b)
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self.lib.crl_calibrate(self._h, planes.data_ptr(), self._layout(planes, layout), b, ws.data_ptr(),
+                                           ws.numel(), s), "calibrate")
+
+    # ---- forward ---------------------------------------------------------------------------------
+    def forward(self, planes, layout="nhwc", legal_mask=None, mask_mode=None, policy=True, wdl=True, q=False,
+                policy_softmax=False, wdl_softmax=True, policy_dtype=torch.float32, host=False):
+        """planes: [..., 8, 8, P] ("nhwc") or [B, P, 8, 8] ("nchw"), on the engine's GPU (or on the host
+        with host=True, which times like a user call: copies in, run, copies out, synchronise).
+        legal_mask: uint8 bitset [B, ceil(V/8)] (bit m of row b: move m legal) or float32 additive [B, V].
+        Returns a dict with `policy` [B, V], `wdl` [B, 3], `q` [B] as requested and available."""
+        planes = planes.contiguous()
+        b = self._batch_of(planes, layout)
+        dev = torch.device("cpu") if host else self.device
+        if planes.device.type != dev.type:
+            raise ValueError(f"planes must live on {dev}")
+        io = L.IO()
+        io.planes = planes.data_ptr()
+        io.layout = self._layout(planes, layout)
+        io.batch = b
+        out = {}
+        if legal_mask is not None:
+            legal_mask = legal_mask.contiguous()
+            if mask_mode is None:
+                mask_mode = L.MASK_BITS if legal_mask.dtype == torch.uint8 else L.MASK_ADDITIVE
+            io.legal_mask = legal_mask.data_ptr()
+            io.mask_mode = mask_mode
+            io.mask_stride = legal_mask.shape[-1]
+        want_policy = policy and self.n_moves > 0
+        kw = dict(device=dev, pin_memory=True) if host else dict(device=dev)
+        if want_policy:
+            out["policy"] = torch.empty(b, self.n_moves, dtype=policy_dtype, **kw)
+            io.policy_out = out["policy"].data_ptr()
+            io.policy_dtype = L.OUT_F32 if policy_dtype == torch.float32 else L.OUT_F16
+            io.policy_softmax = int(policy_softmax)
+            io.policy_stride = self.n_moves
+        if wdl and self.cfg.value_mode != L.VALUE_NONE:
+            out["wdl"] = torch.empty(b, 3, dtype=torch.float32, **kw)
+            io.wdl_out = out["wdl"].data_ptr()
+            io.wdl_softmax = int(wdl_softmax)
+        if q and self.cfg.value_mode == L.VALUE_WDL_Q:
+            out["q"] = torch.empty(b, dtype=torch.float32, **kw)
+            io.q_out = out["q"].data_ptr()
+        io.stream = torch.cuda.current_stream(self.device).cuda_stream
+        if host:
+            self._check(self.lib.crl_forward_host(self._h, ctypes.byref(io)), "forward_host")
+        else:
+            ws = self.workspace(b)
+            io.workspace = ws.data_ptr()
+            io.workspace_bytes = ws.numel()
+            self._check(self.lib.crl_forward(self._h, ctypes.byref(io)), "forward")
+        return out
+
+    def last_status(self):
+        st = ctypes.c_int(0)
+        rc = self.lib.crl_last_status(self._h, ctypes.byref(st))
+        return rc, st.value
+
+    def last_launch_count(self):
+        return int(self.lib.crl_last_launch_count(self._h))

@@ -1,0 +1,180 @@
+"""Drop-in `nn.Module`s: the reference's constructors, `forward` signature and `state_dict` layout
+(new_paradigm/value_q.py:121-211, value.py:121-212), with the arithmetic done by the CUDA engine.
+
+The parameters are ordinary fp32 `nn.Parameter`s under the reference's names, so `state_dict()`,
+`load_state_dict()` and `torch.save` files interchange with the reference. They are storage only: the
+engine keeps its own repacked f16 / e4m3 device copies, refreshed whenever a parameter changed.
+Inference only: `compute_loss=True` (training) is not provided.
+"""
+import torch
+import torch.nn as nn
+
+from . import _lib as L
+from .engine import Engine, EngineConfig
+
+
+def _param_shapes(cfg: EngineConfig):
+    d, ff, h, p = cfg.d_model, cfg.d_ff, cfg.n_heads, cfg.planes
+    hd = d // h
+    shapes = {}
+    for i in range(cfg.n_layers):
+        pre = f"layers.{i}."
+        if cfg.bias_mode == L.BIAS_RELPOS:
+            shapes[pre + "attention.u_bias"] = (h, hd)
+            shapes[pre + "attention.v_bias"] = (h, hd)
+        for n in ("query_proj", "key_proj", "value_proj"):
+            shapes[pre + f"attention.{n}.weight"] = (d, d)
+            shapes[pre + f"attention.{n}.bias"] = (d,)
+        if cfg.bias_mode == L.BIAS_RELPOS:
+            shapes[pre + "attention.pos_proj.weight"] = (d, d)
+        shapes[pre + "attention.out_proj.weight"] = (d, d)
+        shapes[pre + "attention.out_proj.bias"] = (d,)
+        for n in ("norm1", "norm2"):
+            shapes[pre + n + ".weight"] = (d,)
+            shapes[pre + n + ".bias"] = (d,)
+        shapes[pre + "ff1.weight"] = (ff, d)
+        shapes[pre + "ff1.bias"] = (ff,)
+        shapes[pre + "ff2.weight"] = (d, ff)
+        shapes[pre + "ff2.bias"] = (d,)
+        if cfg.bias_mode == L.BIAS_SMOLGEN:
+            c, hid, gen = cfg.smolgen_compress, cfg.smolgen_hidden, cfg.smolgen_gen
+            shapes[pre + "smolgen.compress.weight"] = (c, d)
+            shapes[pre + "smolgen.dense1.weight"] = (hid, 64 * c)
+            shapes[pre + "smolgen.dense1.bias"] = (hid,)
+            shapes[pre + "smolgen.ln1.weight"] = (hid,)
+            shapes[pre + "smolgen.ln1.bias"] = (hid,)
+            shapes[pre + "smolgen.dense2.weight"] = (h * gen, hid)
+            shapes[pre + "smolgen.dense2.bias"] = (h * gen,)
+            shapes[pre + "smolgen.ln2.weight"] = (gen,)
+            shapes[pre + "smolgen.ln2.bias"] = (gen,)
+    shapes["linear1.weight"] = (d, p)
+    shapes["linear1.bias"] = (d,)
+    shapes["layernorm1.weight"] = (d,)
+    shapes["layernorm1.bias"] = (d,)
+    if cfg.policy_mode != L.POLICY_NONE:
+        for n in ("policy_tokens_lin", "queries_pol", "keys_pol"):
+            shapes[n + ".weight"] = (d, d)
+            shapes[n + ".bias"] = (d,)
+    shapes["ma_gating.a"] = (64, d)
+    shapes["ma_gating.b"] = (64, d)
+    if cfg.bias_mode == L.BIAS_SMOLGEN:
+        shapes["smolgen_shared.weight"] = (4096, cfg.smolgen_gen)
+    if cfg.ln_mode == L.LN_PRE:
+        shapes["norm_f.weight"] = (d,)
+        shapes["norm_f.bias"] = (d,)
+    if cfg.policy_mode == L.POLICY_DENSE4096:
+        shapes["policy_head.weight"] = (1929, 4096)
+    if cfg.policy_mode == L.POLICY_GATHER1858:
+        shapes["policy_promo.weight"] = (3, d)
+    heads = []
+    if cfg.value_mode != L.VALUE_NONE:
+        heads.append(("value_head", 3))
+    if cfg.value_mode == L.VALUE_WDL_Q:
+        heads.append(("value_head_q", 1))
+    for name, n_out in heads:
+        shapes[name + ".dense1.weight"] = (128, d)
+        shapes[name + ".dense1.bias"] = (128,)
+        shapes[name + ".dense2.weight"] = (128, 128 * 64)
+        shapes[name + ".dense2.bias"] = (128,)
+        shapes[name + ".dense3.weight"] = (n_out, 128)
+        shapes[name + ".dense3.bias"] = (n_out,)
+    return shapes
+
+
+class _Node(nn.Module):
+    """Container so that dotted reference names (`layers.0.attention.query_proj.weight`) come out of
+    `state_dict()` unchanged."""
+
+
+def _attach(root, dotted, param):
+    parts = dotted.split(".")
+    node = root
+    for part in parts[:-1]:
+        if not hasattr(node, part):
+            node.add_module(part, _Node())
+        node = getattr(node, part)
+    node.register_parameter(parts[-1], param)
+
+
+class BoardTransformer(nn.Module):
+    """Board transformer behind the reference's module protocol. `engine_device` is the GPU index."""
+
+    def __init__(self, cfg: EngineConfig, engine_device=0):
+        super().__init__()
+        self.cfg = cfg
+        self.d_model = cfg.d_model
+        self.num_layers = cfg.n_layers
+        self.is_thinking_model = False                       # value_q.py:124
+        for name, shape in _param_shapes(cfg).items():
+            if name.endswith("norm1.weight") or name.endswith("norm2.weight") or name.endswith("ln1.weight") \
+                    or name.endswith("ln2.weight") or name in ("layernorm1.weight", "norm_f.weight", "ma_gating.b"):
+                init = torch.ones(shape)
+            elif name.endswith(".bias") or name == "ma_gating.a":
+                init = torch.zeros(shape)
+            else:
+                init = torch.randn(shape) * 0.02
+            _attach(self, name, nn.Parameter(init, requires_grad=False))
+        self._engine_device = engine_device
+        self._engine = None
+        self._pushed_versions = None
+
+    # -- engine plumbing ---------------------------------------------------------------------------
+    def engine(self):
+        if self._engine is None:
+            self._engine = Engine(self.cfg, self._engine_device)
+        versions = tuple((p.data_ptr(), p._version) for p in self.parameters())
+        if versions != self._pushed_versions:
+            self._engine.load_state_dict(self.state_dict())
+            self._pushed_versions = versions
+        return self._engine
+
+    def calibrate(self, x):
+        """FP8 engines: x is a batch of planes like the one `forward` takes."""
+        eng = self.engine()
+        eng.calibrate(x.to(eng.device))
+
+    def infer(self, x, **kw):
+        """x: [..., 8, 8, P] planes (any device). Returns the engine's output dict on the GPU."""
+        eng = self.engine()
+        return eng.forward(x.to(eng.device), **kw)
+
+    # -- reference protocol ------------------------------------------------------------------------
+    def forward(self, inp, compute_loss=False):
+        """inp[0]: [b, seq, 8, 8, P] f32 -> policy logits [b, seq, V] (value_q.py:156-211)."""
+        if compute_loss:
+            raise NotImplementedError("inference engine: the training losses are not provided")
+        x = inp[0]
+        b, seq = x.shape[0], x.shape[1]
+        out = self.infer(x, wdl=False)
+        return out["policy"].view(b, seq, -1)
+
+    def position_values(self, x, softmax=True):
+        """Planes -> [B, 3] (black win, draw, white win) as in get_batch_position_values
+        (value.py:275-317), which softmaxes the value logits (value.py:315)."""
+        return self.infer(x, policy=False, wdl=True, wdl_softmax=softmax)["wdl"]
+
+
+class BT4(BoardTransformer):
+    """`BT4(num_layers, d_model, d_ff, num_heads)` of new_paradigm/value_q.py:121-153: 112 input
+    planes, relative attention, dense 4096 -> 1929 policy, WDL and Q value heads."""
+
+    def __init__(self, num_layers=10, d_model=512, d_ff=736, num_heads=8, dtype=L.DTYPE_F16, engine_device=0):
+        super().__init__(EngineConfig.reference_value_q(num_layers, d_model, d_ff, num_heads, dtype=dtype),
+                         engine_device)
+
+
+class BT4Planes19(BoardTransformer):
+    """`BT4` of new_paradigm/value.py:121-153: 19 input planes (utils/fen_encoder.py:5-38), WDL head."""
+
+    def __init__(self, num_layers=10, d_model=512, d_ff=736, num_heads=8, dtype=L.DTYPE_F16, engine_device=0):
+        super().__init__(EngineConfig.reference_value(num_layers, d_model, d_ff, num_heads, dtype=dtype),
+                         engine_device)
+
+
+class BT4Baseline(BoardTransformer):
+    """The network of the target specification (smolgen bias, Mish FFN, 1858-move gather policy)."""
+
+    def __init__(self, num_layers=15, d_model=1024, d_ff=1536, num_heads=32, smolgen=True, value_only=False,
+                 dtype=L.DTYPE_F16, engine_device=0, chunk=0):
+        super().__init__(EngineConfig.baseline(num_layers, d_model, d_ff, num_heads, smolgen=smolgen,
+                                               value_only=value_only, dtype=dtype, chunk=chunk), engine_device)

@@ -1,0 +1,145 @@
+/* chessrl_b200 - C ABI of the B200 board-transformer inference engine.
+ *
+ * The reference (maxlegrec1/ChessRL) has no FFI: its boundary is the PyTorch nn.Module protocol
+ * (constructor, forward, state_dict). Each entry point below names the reference interface it stands
+ * behind. All pointers are plain device or host addresses; nothing here depends on torch. Functions
+ * return 0 on success or a negative crl_status; nothing is printed or thrown; kernels never trap:
+ * device-side waits are bounded and report through crl_last_status.
+ *
+ * Threading: a handle is bound to one CUDA device and is not re-entrant; use one handle per GPU.
+ */
+#ifndef CHESSRL_B200_H_
+#define CHESSRL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct crl_handle crl_handle;
+
+enum crl_status {
+  CRL_OK = 0,
+  CRL_ERR_INVALID = -1,        /* null pointer, negative size, unknown enum value */
+  CRL_ERR_SHAPE = -2,          /* shape / alignment the kernels cannot take */
+  CRL_ERR_CUDA = -3,           /* a CUDA call failed (crl_error_detail has the text) */
+  CRL_ERR_MISSING_WEIGHT = -4, /* finalize: a state_dict key the configuration needs was never set */
+  CRL_ERR_NOT_FINALIZED = -5,
+  CRL_ERR_DEVICE_TIMEOUT = -6, /* a bounded device-side wait ran out; see crl_last_status */
+  CRL_ERR_WORKSPACE = -7,      /* workspace too small */
+  CRL_ERR_UNSUPPORTED = -8
+};
+
+enum { CRL_LN_POST = 0, CRL_LN_PRE = 1 };
+enum { CRL_ACT_GELU = 1, CRL_ACT_MISH = 2 };
+enum { CRL_FFN_ACT_END = 0, CRL_FFN_ACT_MID = 1 };
+enum { CRL_BIAS_NONE = 0, CRL_BIAS_CAUSAL = 1, CRL_BIAS_RELPOS = 2, CRL_BIAS_SMOLGEN = 3 };
+enum { CRL_POLICY_NONE = 0, CRL_POLICY_DENSE4096 = 1, CRL_POLICY_GATHER1858 = 2 };
+enum { CRL_VALUE_NONE = 0, CRL_VALUE_WDL = 1, CRL_VALUE_WDL_Q = 2 };
+enum { CRL_DTYPE_F16 = 0, CRL_DTYPE_F8E4M3 = 1, CRL_DTYPE_I8 = 2 };
+enum { CRL_LAYOUT_NHWC_F32 = 0, CRL_LAYOUT_NHWC_F16 = 1, CRL_LAYOUT_NCHW_F16 = 2, CRL_LAYOUT_NCHW_F32 = 3 };
+enum { CRL_MASK_NONE = 0, CRL_MASK_BITS = 1, CRL_MASK_ADDITIVE = 2 };
+enum { CRL_OUT_F32 = 0, CRL_OUT_F16 = 1 };
+
+/* Network description. Stands for the reference constructors
+ *   BT4(num_layers, d_model, d_ff, num_heads)      new_paradigm/value.py:122, value_q.py:122
+ * (planes 19 / 112 are fixed per class there: value.py:132, value_q.py:132); the remaining fields select
+ * the variants of the target specification (Mish, activation position, pre-LN, smolgen, gather policy)
+ * and the arithmetic type of the QKV / out-proj / FFN GEMMs. */
+typedef struct crl_config {
+  int32_t planes;
+  int32_t d_model;
+  int32_t n_layers;
+  int32_t n_heads;
+  int32_t d_ff;
+  int32_t ln_mode;
+  int32_t act;
+  int32_t ffn_act_pos;
+  int32_t bias_mode;
+  int32_t policy_mode;
+  int32_t value_mode;
+  int32_t dtype;
+  int32_t smolgen_compress; /* 32 */
+  int32_t smolgen_hidden;   /* 256 */
+  int32_t smolgen_gen;      /* 256 */
+  int32_t chunk;            /* positions processed per pass over the layers; 0 = library default */
+} crl_config;
+
+/* One forward call. Stands for BT4.forward / get_batch_position_values (new_paradigm/value.py:155-212,
+ * 275-317) and the server's bt4(X)['policy'] + mask + softmax (Leela/server.py:28-34,54-56).
+ * Every pointer is a DEVICE pointer for crl_forward and a HOST pointer for crl_forward_host. */
+typedef struct crl_io {
+  const void* planes;      /* input planes in `layout`, `batch` positions */
+  int32_t layout;
+  int64_t batch;
+  const void* legal_mask;  /* nullable. BITS: u8 [batch, mask_stride] bit m of a row = move m legal,
+                              applied as logits + (1-bit)*(-999) (model_bis.py:383); ADDITIVE: f32
+                              [batch, mask_stride] added to the logits (server.py:56) */
+  int32_t mask_mode;
+  int64_t mask_stride;     /* bytes per row (BITS) or floats per row (ADDITIVE) */
+  void* policy_out;        /* nullable. [batch, policy_stride] logits (or probabilities) */
+  int32_t policy_dtype;    /* CRL_OUT_F32 / CRL_OUT_F16 */
+  int32_t policy_softmax;  /* 1: softmax over the (masked) logits */
+  int64_t policy_stride;   /* elements per row, >= number of moves */
+  float* wdl_out;          /* nullable. [batch, 3] */
+  int32_t wdl_softmax;     /* 1: probabilities (value.py:271), 0: raw logits */
+  float* q_out;            /* nullable. [batch] tanh value (value_q.py:430-464), value_mode WDL_Q only */
+  void* workspace;         /* device scratch, >= crl_workspace_bytes(h, batch) (ignored by _host) */
+  size_t workspace_bytes;
+  void* stream;            /* cudaStream_t, may be null (default stream) */
+} crl_io;
+
+/* Constructor: replaces BT4.__init__ (value.py:122-153). The device must be a B200 (sm_100). */
+int crl_create(const crl_config* cfg, int device, crl_handle** out);
+void crl_destroy(crl_handle* h);
+
+/* load_state_dict: one call per state_dict entry, with the reference's key names
+ * (layers.{i}.attention.query_proj.weight, ..., linear1.weight, ma_gating.a, value_head.dense1.weight;
+ * listed by crl_required_key). `data` is f32, host or device memory, row-major, `numel` elements. */
+int crl_set_weight(crl_handle* h, const char* key, const float* data, int64_t numel);
+/* Number of keys the configuration needs, and the i-th key (null past the end). */
+int crl_num_required_keys(const crl_handle* h);
+const char* crl_required_key(const crl_handle* h, int i);
+/* Repack once: f16 (and e4m3 / int8 + scales) device copies, fused QKV, folded positional tables. */
+int crl_finalize(crl_handle* h);
+
+/* FP8 only: per-tensor activation scales from a calibration batch (device pointer), the static
+ * equivalent of the reference's delayed scaling recipe (pretrain_fp8.py:75-79: E4M3, margin 0). */
+int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t batch, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+size_t crl_workspace_bytes(const crl_handle* h, int64_t batch);
+int crl_num_moves(const crl_handle* h); /* 1929 (dense policy), 1858 (gather policy), 0 (none) */
+
+int crl_forward(crl_handle* h, const crl_io* io);
+/* Same call with HOST buffers: copies the planes (and mask) to the device, runs, copies results back and
+ * synchronises. Staging buffers and workspace are owned by the handle and grow on demand. */
+int crl_forward_host(crl_handle* h, const crl_io* io);
+
+/* Reads and clears the device status word (0 = fine, 101/102/103 = a bounded wait of the GEMM's
+ * producer / MMA / epilogue role ran out). Synchronises the device. */
+int crl_last_status(crl_handle* h, int* device_status_word);
+/* Number of kernels the last crl_forward launched. */
+int64_t crl_last_launch_count(const crl_handle* h);
+const char* crl_error_detail(const crl_handle* h);
+const char* crl_strerror(int status);
+
+/* Operator-level entry (tests, tuning): C = act(alpha * A W^T + bias) + residual on device buffers.
+ * kind: CRL_DTYPE_* of A and W (f16, e4m3, int8); out_dtype: 0 f16, 1 f32, 2 e4m3. Stands for one
+ * nn.Linear call (e.g. new_paradigm/value.py:65-67). */
+int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw, void* c, int64_t ldc,
+               int out_dtype, int64_t m, int64_t n, int64_t k, const float* bias, const void* residual,
+               int64_t ldr, float alpha, int act, int* device_status, void* stream);
+
+/* Move vocabulary (utils/vocab.py:9-438): writes the UCI string of entry `index` of the 1929-entry
+ * list into buf (>= 16 bytes); entries < 1858 are the Leela list. Returns 0, or CRL_ERR_INVALID. */
+int crl_vocab_move(int index, char* buf);
+/* Index in the 1929 list of the rank-mirrored Leela move `leela_index` (compare_policy.py:465-483). */
+int crl_vocab_mirror_index(int leela_index);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHESSRL_B200_H_ */

@@ -294,13 +294,14 @@ class BT4Spec(nn.Module):
 
 
 def seeded_state_dict(module, seed=0, std=0.02):
-    """Every parameter ~ N(0, std) drawn in state_dict key order from one seeded CPU generator; LayerNorm
+    """Every parameter ~ N(0, std) drawn in sorted key order from one seeded CPU generator; LayerNorm
     weights 1 / biases 0 and the gating a=0, b=1 keep their constructor values."""
     g = torch.Generator().manual_seed(seed)
     sd = module.state_dict()
     keep = ("norm1.", "norm2.", "layernorm1.", "ln1.", "ln2.", "norm_f.", "ma_gating.", "ln_1.", "ln_2.",
             "ln_f.")
-    for k, v in sd.items():
+    for k in sorted(sd.keys()):
+        v = sd[k]
         if any(t in k for t in keep):
             continue
         sd[k] = torch.randn(v.shape, generator=g) * std

@@ -58,11 +58,11 @@ def synthetic_tokens(batch, planes, seed):
 def run_case(name, ref_cls, spec_cfg, dims, batch, seed, head_q):
     model = ref_cls(*dims)
     spec = bt4spec.BT4Spec(spec_cfg)
-    assert list(model.state_dict().keys()) == list(spec.state_dict().keys()), "state_dict keys differ"
+    assert sorted(model.state_dict().keys()) == sorted(spec.state_dict().keys()), "state_dict keys differ"
     sd = bt4spec.seeded_state_dict(spec, seed=seed)
     # non-trivial LayerNorm / gating parameters so that those code paths are pinned as well
     g = torch.Generator().manual_seed(seed + 1)
-    for k in sd:
+    for k in sorted(sd):
         if k.endswith("ma_gating.a"):
             sd[k] = torch.randn(sd[k].shape, generator=g) * 0.1
         elif "norm" in k and k.endswith("weight"):

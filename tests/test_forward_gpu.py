@@ -1,0 +1,188 @@
+"""Parity of the CUDA engine (through the C ABI) against the CPU oracle and the reference fixtures.
+
+Tolerances are the ones the target states: FP16 policy-logit max-abs error <= 2e-2 and WDL
+probabilities within 1e-2 of the FP32 reference; masks and indices are exact."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from oracle import bt4spec, vocab
+
+pytestmark = pytest.mark.gpu
+
+POLICY_TOL = 2e-2
+WDL_TOL = 1e-2
+
+
+def engine_cfg(spec_cfg, **kw):
+    from chessrl_b200 import EngineConfig
+    return EngineConfig(dtype=kw.pop("dtype", 0), chunk=kw.pop("chunk", 0), **spec_cfg.to_dict())
+
+
+def random_tokens(batch, planes, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.rand(batch, 64, planes, generator=g) < 0.08).float()
+    x[:, :, planes - 1] = 1.0
+    x[:, :, planes - 3] = (torch.rand(batch, 1, generator=g) * 0.5).half().float().expand(batch, 64)
+    return x
+
+
+def oracle_out(spec_cfg, sd, tokens):
+    spec = bt4spec.BT4Spec(spec_cfg)
+    spec.load_state_dict(sd)
+    spec.eval()
+    with torch.no_grad():
+        return spec.forward_all(tokens)
+
+
+def run_engine(spec_cfg, sd, tokens, **fw):
+    from chessrl_b200 import Engine
+    eng = Engine(engine_cfg(spec_cfg, dtype=fw.pop("dtype", 0), chunk=fw.pop("chunk", 0)))
+    eng.load_state_dict(sd)
+    x = tokens.view(tokens.shape[0], 8, 8, -1).cuda()
+    out = eng.forward(x, **fw)
+    torch.cuda.synchronize()
+    rc, st = eng.last_status()
+    assert rc == 0 and st == 0, f"device status {st}"
+    assert eng.last_launch_count() > 0
+    return {k: v.float().cpu() for k, v in out.items()}, eng
+
+
+CASES = sorted(glob.glob(os.path.join(GOLDEN, "ref_*.npz")))
+
+
+@pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[:-4] for p in CASES])
+def test_reference_fixture(path):
+    """Engine vs outputs of the unmodified reference module (relative attention, dense 1929 policy)."""
+    from test_oracle_golden import golden_state_dict, spec_for
+    z = np.load(path)
+    dims = [int(v) for v in z["dims"]]
+    cfg = spec_for(os.path.basename(path), dims)
+    sd = golden_state_dict(bt4spec.BT4Spec(cfg), int(z["seed"]))
+    tokens = torch.from_numpy(z["tokens"]).float()
+    out, _ = run_engine(cfg, sd, tokens, wdl_softmax=False, q="q" in z.files)
+    assert (out["policy"] - torch.from_numpy(z["policy"])).abs().max() <= POLICY_TOL
+    assert (out["wdl"] - torch.from_numpy(z["wdl"])).abs().max() <= POLICY_TOL
+    probs = torch.softmax(out["wdl"], -1)
+    assert (probs - torch.softmax(torch.from_numpy(z["wdl"]), -1)).abs().max() <= WDL_TOL
+    if "q" in z.files:
+        assert (out["q"].view(-1) - torch.from_numpy(z["q"]).view(-1)).abs().max() <= WDL_TOL
+
+
+@pytest.mark.parametrize("name,cfg,batch", [
+    ("c2_small_gather", bt4spec.SpecConfig.baseline(8, 256, 1024, 8, smolgen=False), 5),
+    ("c2_small_smolgen", bt4spec.SpecConfig.baseline(2, 256, 1024, 8, smolgen=True), 3),
+    ("bt4_shape_2layers", bt4spec.SpecConfig.baseline(2, 1024, 1536, 32, smolgen=True), 3),
+    ("prelN_gelu_end", bt4spec.SpecConfig(112, 256, 2, 8, 512, bt4spec.LN_PRE, bt4spec.ACT_GELU, bt4spec.FFN_ACT_END,
+                                          bt4spec.BIAS_NONE, bt4spec.POLICY_GATHER1858, bt4spec.VALUE_WDL), 2),
+    ("hd64_relpos", bt4spec.SpecConfig.reference_value_q(2, 512, 736, 8), 2),
+    ("value_only", bt4spec.SpecConfig.baseline(2, 256, 1024, 8, smolgen=True, value_only=True), 4),
+])
+def test_against_oracle(name, cfg, batch):
+    torch.manual_seed(0)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=3)
+    tokens = random_tokens(batch, cfg.planes, seed=5)
+    ref = oracle_out(cfg, sd, tokens)
+    out, _ = run_engine(cfg, sd, tokens, wdl_softmax=True)
+    if "policy" in ref:
+        assert (out["policy"] - ref["policy"]).abs().max() <= POLICY_TOL
+        assert torch.equal(out["policy"].argmax(-1), ref["policy"].argmax(-1)) or \
+            (out["policy"] - ref["policy"]).abs().max() <= 2e-3
+    else:
+        assert "policy" not in out
+    assert (out["wdl"] - torch.softmax(ref["wdl"], -1)).abs().max() <= WDL_TOL
+
+
+def test_chunking_and_ragged_batch_are_invisible():
+    """A batch that is not a multiple of the chunk, processed in several passes, equals one pass."""
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=4)
+    tokens = random_tokens(11, cfg.planes, seed=6)
+    one, _ = run_engine(cfg, sd, tokens, chunk=64)
+    many, _ = run_engine(cfg, sd, tokens, chunk=4)
+    assert torch.equal(one["policy"], many["policy"]) and torch.equal(one["wdl"], many["wdl"])
+
+
+def test_legal_mask_conventions_exact():
+    """logits + (1-mask)*(-999) for a bitset (model_bis.py:383) and mask_vec + logits with -1000/0
+    (Leela/server.py:56): the masked index set is exact, softmax mass on illegal moves vanishes."""
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=False)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=7)
+    b = 6
+    tokens = random_tokens(b, cfg.planes, seed=8)
+    g = torch.Generator().manual_seed(9)
+    legal = torch.rand(b, 1858, generator=g) < 0.02
+    legal[:, 0] = True
+    bits = np.packbits(legal.numpy(), axis=1, bitorder="little")
+    bits_t = torch.from_numpy(bits).cuda()
+    raw, eng = run_engine(cfg, sd, tokens)
+    x = tokens.view(b, 8, 8, -1).cuda()
+    masked = eng.forward(x, legal_mask=bits_t)["policy"].cpu()
+    expect = raw["policy"] + (1 - legal.float()) * -999
+    assert torch.equal(masked, expect)
+    additive = ((~legal).float() * -1000.0).cuda()
+    probs = eng.forward(x, legal_mask=additive, policy_softmax=True)["policy"].cpu()
+    ref = torch.softmax(raw["policy"] + additive.cpu(), -1)
+    assert (probs - ref).abs().max() < 1e-5
+    assert torch.equal(probs > 0, legal) or float(probs[~legal].max()) == 0.0
+    assert torch.equal(probs.argmax(-1), ref.argmax(-1))
+
+
+def test_input_layouts_agree():
+    """[B,8,8,P] f32 (module signature), the same in f16, and [B,P,8,8] f16 (server) give one result."""
+    cfg = bt4spec.SpecConfig.baseline(1, 256, 512, 8, smolgen=False)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=10)
+    tokens = random_tokens(3, cfg.planes, seed=11)
+    a, eng = run_engine(cfg, sd, tokens)
+    x = tokens.view(3, 8, 8, -1).cuda()
+    b = eng.forward(x.half())["policy"].cpu()
+    c = eng.forward(x.half().permute(0, 3, 1, 2).contiguous(), layout="nchw")["policy"].cpu()
+    assert torch.equal(a["policy"], b) and torch.equal(a["policy"], c)
+
+
+def test_host_entry_point_matches_device_entry_point():
+    cfg = bt4spec.SpecConfig.baseline(1, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=12)
+    tokens = random_tokens(4, cfg.planes, seed=13)
+    dev, eng = run_engine(cfg, sd, tokens)
+    host = eng.forward(tokens.view(4, 8, 8, -1).half().pin_memory(), host=True)
+    assert torch.equal(dev["policy"], host["policy"]) and torch.equal(dev["wdl"], host["wdl"])
+
+
+def test_module_drop_in_round_trips_state_dict():
+    """The nn.Module keeps the reference's key names and shapes and serves `forward(inp)`."""
+    from chessrl_b200 import BT4
+    cfg = bt4spec.SpecConfig.reference_value_q(2, 256, 320, 8)
+    spec = bt4spec.BT4Spec(cfg)
+    sd = bt4spec.seeded_state_dict(spec, seed=14)
+    model = BT4(2, 256, 320, 8)
+    assert {k: tuple(v.shape) for k, v in model.state_dict().items()} == {k: tuple(v.shape) for k, v in sd.items()}
+    model.load_state_dict(sd)
+    tokens = random_tokens(2, 112, seed=15)
+    pol = model([tokens.view(2, 1, 8, 8, 112), None])
+    assert pol.shape == (2, 1, 1929)
+    ref = oracle_out(cfg, sd, tokens)
+    assert (pol.view(2, -1).cpu() - ref["policy"]).abs().max() <= POLICY_TOL
+    vals = model.position_values(tokens.view(2, 8, 8, 112)).cpu()
+    assert (vals - torch.softmax(ref["wdl"], -1)).abs().max() <= WDL_TOL
+
+
+def test_errors_are_reported_not_thrown_across_the_abi():
+    from chessrl_b200 import Engine, CrlError
+    cfg = bt4spec.SpecConfig.baseline(1, 256, 512, 8, smolgen=False)
+    eng = Engine(engine_cfg(cfg))
+    with pytest.raises(CrlError) as e:
+        eng.forward(torch.zeros(1, 8, 8, 112, device="cuda"))
+    assert e.value.code == -5                      # not finalized
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=1)
+    missing = dict(sd)
+    del missing["ma_gating.a"]
+    with pytest.raises(CrlError) as e:
+        eng.load_state_dict(missing)
+    assert e.value.code == -4 and "ma_gating.a" in str(e.value)
+    eng.load_state_dict(sd)
+    assert eng.forward(torch.zeros(0, 8, 8, 112, device="cuda"))["policy"].shape == (0, 1858)   # empty batch
