@@ -60,6 +60,11 @@ struct crl_handle {
   int* status_dev = nullptr;
   unsigned int* amax_dev = nullptr;   // [L*4] float bit patterns
   int64_t launches = 0;
+  // optional per-kernel timing (crl_profile): event pairs around every launch, by category
+  struct ProfRec { cudaEvent_t a, b; int cat; double flops, bytes; };
+  std::vector<ProfRec> prof;
+  size_t prof_used = 0;
+  bool profiling = false;
 
   __half *w_embed = nullptr, *pe16 = nullptr, *sg_shared = nullptr, *w_pt = nullptr, *w_qk = nullptr, *w_ph = nullptr;
   float *b_embed = nullptr, *lnE_w = nullptr, *lnE_b = nullptr, *gate_ea = nullptr, *gate_b = nullptr;
@@ -229,6 +234,25 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc) {
 }
 
 // ---- launch helpers --------------------------------------------------------------------------------
+enum ProfCat : int { kCatGemm = 0, kCatAttention = 1, kCatLayerNorm = 2, kCatOther = 3 };
+
+// Brackets one launch with CUDA events on the launch stream while profiling is on.
+struct ProfScope {
+  crl_handle* h; cudaStream_t s; crl_handle::ProfRec* rec = nullptr;
+  ProfScope(crl_handle* h_, cudaStream_t s_, int cat, double flops, double bytes) : h(h_), s(s_) {
+    if (!h->profiling) return;
+    if (h->prof_used == h->prof.size()) {
+      crl_handle::ProfRec r{};
+      if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+      h->prof.push_back(r);
+    }
+    rec = &h->prof[h->prof_used++];
+    rec->cat = cat; rec->flops = flops; rec->bytes = bytes;
+    cudaEventRecord(rec->a, s);
+  }
+  ~ProfScope() { if (rec != nullptr) cudaEventRecord(rec->b, s); }
+};
+
 struct Lin {
   int kind = kKindF16;
   const void* a = nullptr; long long lda = 0;
@@ -249,6 +273,10 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.bias = l.bias; g.p.residual = l.res; g.p.ldr = l.ldr; g.p.res_mod = l.res_mod;
   g.p.alpha = l.alpha; g.p.row_scale = nullptr; g.p.col_scale = nullptr;
   g.p.act = l.act; g.p.out_scale = l.out_scale; g.p.status = h->status_dev;
+  const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
+  ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
+               static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
+                   static_cast<double>(l.m) * l.n * esz_out + (l.res != nullptr && l.res_mod == 0 ? 2.0 * l.m * l.n : 0.0));
   const int rc = gemm_launch(g, h->num_sms, s);
   if (rc != kOk) return fail(h, rc, "gemm launch failed (M=" + std::to_string(l.m) + " N=" + std::to_string(l.n) +
                                         " K=" + std::to_string(l.k) + ")");
@@ -263,6 +291,7 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
   p.gate_ea = gate_ea; p.gate_b = gate_b;
   p.y = y; p.ldy = d; p.y8 = y8; p.ldy8 = d; p.out8_scale = y8_scale;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * d * (2 + (y != nullptr ? 2 : 0) + (y8 != nullptr ? 1 : 0)));
   ln_rows_kernel<<<blocks, 256, 0, s>>>(p);
   CRL_CUDA(h, cudaGetLastError());
   ++h->launches;
@@ -381,6 +410,9 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       a.ldo = d;
       if (f8) { a.out = nullptr; a.out8 = w.t2_8; a.out8_scale = L.sa_ctx; }
       else { a.out = w.t2; a.out8 = nullptr; a.out8_scale = 1.0f; }
+      ProfScope ps(h, s, kCatAttention, 4.0 * M * 64 * d,
+                   static_cast<double>(M) * d * 2 * 3 + static_cast<double>(M) * d * (f8 ? 1 : 2) +
+                       (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * 8192 : 0.0));
       CRL_CUDA(h, attention_launch(a, h->hd, c.bias_mode, s));
       ++h->launches;
     }
@@ -462,6 +494,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       p.mask = mask_row; p.mask_mode = mask_mode; p.mask_ld = io->mask_stride; p.softmax = io->policy_softmax;
       p.out_f32 = out32; p.out_f16 = out16; p.out_ld = io->policy_stride;
     }
+    ProfScope ps(h, s, kCatOther, 2.0 * bc * 64 * 64 * d, static_cast<double>(M) * 2 * d * 2 + static_cast<double>(bc) * n_moves * 4);
     policy_scores_kernel<<<static_cast<unsigned>(bc), 128, 0, s>>>(p);
     CRL_CUDA(h, cudaGetLastError());
     ++h->launches;
@@ -611,6 +644,7 @@ void crl_destroy(crl_handle* h) {
   if (h == nullptr) return;
   cudaSetDevice(h->device);
   for (void* p : h->allocs) cudaFree(p);
+  for (auto& r : h->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
   for (void* p : {h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
     if (p != nullptr) cudaFree(p);
   delete h;
@@ -898,6 +932,28 @@ int crl_last_status(crl_handle* h, int* device_status_word) {
 }
 
 int64_t crl_last_launch_count(const crl_handle* h) { return h != nullptr ? h->launches : 0; }
+
+int crl_profile(crl_handle* h, int enable) {
+  if (h == nullptr) return CRL_ERR_INVALID;
+  h->profiling = enable != 0;
+  h->prof_used = 0;
+  return CRL_OK;
+}
+
+int crl_profile_read(crl_handle* h, int category, double* ms, double* flops, double* bytes, int64_t* launches) {
+  if (h == nullptr || ms == nullptr || flops == nullptr || bytes == nullptr || launches == nullptr) return CRL_ERR_INVALID;
+  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_CUDA(h, cudaDeviceSynchronize());
+  *ms = 0.0; *flops = 0.0; *bytes = 0.0; *launches = 0;
+  for (size_t i = 0; i < h->prof_used; ++i) {
+    const auto& r = h->prof[i];
+    if (r.cat != category) continue;
+    float t = 0.0f;
+    CRL_CUDA(h, cudaEventElapsedTime(&t, r.a, r.b));
+    *ms += t; *flops += r.flops; *bytes += r.bytes; ++*launches;
+  }
+  return CRL_OK;
+}
 
 int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw, void* c, int64_t ldc, int out_dtype,
                int64_t m, int64_t n, int64_t k, const float* bias, const void* residual, int64_t ldr, float alpha,

@@ -190,3 +190,17 @@ class Engine:
 
     def last_launch_count(self):
         return int(self.lib.crl_last_launch_count(self._h))
+
+    def profile(self, enable=True):
+        """Turn per-kernel event timing on (clearing earlier records) or off."""
+        self._check(self.lib.crl_profile(self._h, int(enable)), "profile")
+
+    def profile_read(self):
+        """{category: dict(ms, flops, bytes, launches)} summed over the launches recorded since profile(True)."""
+        out = {}
+        for cat, name in enumerate(("gemm", "attention", "layernorm", "policy")):
+            ms, fl, by, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_double(), ctypes.c_int64()
+            self._check(self.lib.crl_profile_read(self._h, cat, ctypes.byref(ms), ctypes.byref(fl), ctypes.byref(by),
+                                                  ctypes.byref(n)), "profile_read")
+            out[name] = dict(ms=ms.value, flops=fl.value, bytes=by.value, launches=n.value)
+        return out

@@ -123,6 +123,13 @@ int crl_forward_host(crl_handle* h, const crl_io* io);
 int crl_last_status(crl_handle* h, int* device_status_word);
 /* Number of kernels the last crl_forward launched. */
 int64_t crl_last_launch_count(const crl_handle* h);
+/* Per-kernel timing for roofline reports (no reference counterpart; the reference has no profiler hooks,
+ * only time.time() deltas in Leela/test_inference.py:16-33). While enabled, every launch of crl_forward is
+ * bracketed by CUDA events on the launch stream. crl_profile(h, 1) also clears earlier records.
+ * Categories: 0 tcgen05 GEMMs, 1 attention, 2 LayerNorm, 3 policy scores. crl_profile_read synchronises
+ * and returns summed device time, algorithmic FLOPs and algorithmic bytes of that category. */
+int crl_profile(crl_handle* h, int enable);
+int crl_profile_read(crl_handle* h, int category, double* ms, double* flops, double* bytes, int64_t* launches);
 const char* crl_error_detail(const crl_handle* h);
 const char* crl_strerror(int status);
 

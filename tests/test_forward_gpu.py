@@ -186,3 +186,30 @@ def test_errors_are_reported_not_thrown_across_the_abi():
     assert e.value.code == -4 and "ma_gating.a" in str(e.value)
     eng.load_state_dict(sd)
     assert eng.forward(torch.zeros(0, 8, 8, 112, device="cuda"))["policy"].shape == (0, 1858)   # empty batch
+
+
+def test_fp8_engine_tolerances():
+    """FP8 e4m3 (per-tensor weight and calibrated activation scales on the QKV / out-proj / FFN GEMMs)
+    against the FP32 oracle: top-1 move agreement >= 99 %, WDL within 3e-2."""
+    cfg = bt4spec.SpecConfig.baseline(8, 256, 1024, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=21)
+    b = 256
+    tokens = random_tokens(b, cfg.planes, seed=22)
+    ref = oracle_out(cfg, sd, tokens)
+    from chessrl_b200 import Engine
+    eng = Engine(engine_cfg(cfg, dtype=1))
+    eng.load_state_dict(sd)
+    x = tokens.view(b, 8, 8, -1).cuda()
+    from chessrl_b200 import CrlError
+    with pytest.raises(CrlError):
+        eng.forward(x)                                  # FP8 needs calibration first
+    eng.calibrate(x[:64])
+    out = eng.forward(x)
+    rc, st = eng.last_status()
+    assert rc == 0 and st == 0
+    pol, wdl = out["policy"].cpu(), out["wdl"].cpu()
+    agree = (pol.argmax(-1) == ref["policy"].argmax(-1)).float().mean().item()
+    werr = (wdl - torch.softmax(ref["wdl"], -1)).abs().max().item()
+    perr = (pol - ref["policy"]).abs().max().item()
+    print(f"fp8: top-1 agreement {agree:.4f}, wdl err {werr:.3e}, policy max-abs err {perr:.3e}")
+    assert agree >= 0.99 and werr <= 3e-2
