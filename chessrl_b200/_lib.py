@@ -25,7 +25,7 @@ EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
-    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read",
+    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry",
 ]
 
 
@@ -93,6 +93,10 @@ def load():
     lib.crl_profile_read.argtypes = [vp, ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
                                      ctypes.POINTER(ctypes.c_double), ctypes.POINTER(i64)]
     lib.crl_profile_read.restype = ctypes.c_int
+    lib.crl_profile_entry.argtypes = [vp, i64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_double),
+                                      ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
+                                      ctypes.POINTER(ctypes.c_int * 4)]
+    lib.crl_profile_entry.restype = ctypes.c_int
     lib.crl_error_detail.argtypes = [vp]
     lib.crl_error_detail.restype = ctypes.c_char_p
     lib.crl_strerror.argtypes = [ctypes.c_int]

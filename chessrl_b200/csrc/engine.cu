@@ -61,7 +61,7 @@ struct crl_handle {
   unsigned int* amax_dev = nullptr;   // [L*4] float bit patterns
   int64_t launches = 0;
   // optional per-kernel timing (crl_profile): event pairs around every launch, by category
-  struct ProfRec { cudaEvent_t a, b; int cat; double flops, bytes; };
+  struct ProfRec { cudaEvent_t a, b; int cat; double flops, bytes; int m, n, k, kind; };
   std::vector<ProfRec> prof;
   size_t prof_used = 0;
   bool profiling = false;
@@ -247,7 +247,7 @@ struct ProfScope {
       h->prof.push_back(r);
     }
     rec = &h->prof[h->prof_used++];
-    rec->cat = cat; rec->flops = flops; rec->bytes = bytes;
+    rec->cat = cat; rec->flops = flops; rec->bytes = bytes; rec->m = rec->n = rec->k = rec->kind = 0;
     cudaEventRecord(rec->a, s);
   }
   ~ProfScope() { if (rec != nullptr) cudaEventRecord(rec->b, s); }
@@ -277,6 +277,7 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
                static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
                    static_cast<double>(l.m) * l.n * esz_out + (l.res != nullptr && l.res_mod == 0 ? 2.0 * l.m * l.n : 0.0));
+  if (ps.rec != nullptr) { ps.rec->m = static_cast<int>(l.m); ps.rec->n = l.n; ps.rec->k = l.k; ps.rec->kind = l.kind; }
   const int rc = gemm_launch(g, h->num_sms, s);
   if (rc != kOk) return fail(h, rc, "gemm launch failed (M=" + std::to_string(l.m) + " N=" + std::to_string(l.n) +
                                         " K=" + std::to_string(l.k) + ")");
@@ -937,6 +938,20 @@ int crl_profile(crl_handle* h, int enable) {
   if (h == nullptr) return CRL_ERR_INVALID;
   h->profiling = enable != 0;
   h->prof_used = 0;
+  return CRL_OK;
+}
+
+int crl_profile_entry(crl_handle* h, int64_t index, int* category, double* ms, double* flops, double* bytes, int* mnk_kind) {
+  if (h == nullptr || category == nullptr || ms == nullptr || flops == nullptr || bytes == nullptr || mnk_kind == nullptr)
+    return CRL_ERR_INVALID;
+  if (index < 0 || static_cast<size_t>(index) >= h->prof_used) return CRL_ERR_INVALID;
+  CRL_CUDA(h, cudaSetDevice(h->device));
+  const auto& r = h->prof[index];
+  CRL_CUDA(h, cudaEventSynchronize(r.b));
+  float t = 0.0f;
+  CRL_CUDA(h, cudaEventElapsedTime(&t, r.a, r.b));
+  *category = r.cat; *ms = t; *flops = r.flops; *bytes = r.bytes;
+  mnk_kind[0] = r.m; mnk_kind[1] = r.n; mnk_kind[2] = r.k; mnk_kind[3] = r.kind;
   return CRL_OK;
 }
 

@@ -8,8 +8,9 @@
 //   warp 1      : MMA issuer    - one thread issues tcgen05.mma (128 x BN x 32-byte-K) with fp32
 //                 (int32 for int8) accumulators in tensor memory; two accumulator buffers so the
 //                 next tile's main loop overlaps this tile's epilogue
-//   warps 2..5  : epilogue      - tcgen05.ld of the accumulator (each warp owns the 32 TMEM lanes
-//                 its rank allows), then scale / bias / activation / residual, convert, store
+//   warps 2..9  : epilogue      - tcgen05.ld of the accumulator (a warp may read the 32 TMEM lanes
+//                 its rank modulo 4 selects; two warps share a lane quarter and split the columns),
+//                 then scale / bias / activation / residual, convert, store
 // All waits are bounded (see ptx.cuh); a wait that runs out records a status code and unwinds.
 #pragma once
 #include <cuda_runtime.h>
@@ -36,6 +37,8 @@ struct GemmParams {
   int* status;             // device status word
 };
 
+constexpr int kGemmThreads = 320;   // TMA warp + MMA warp + 8 epilogue warps
+
 template <int BN, int KIND>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -47,7 +50,10 @@ struct GemmCfg {
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
-  static constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+  // after the stages: 256 bytes of mbarriers + TMEM slot, the bias table [2][BN] f32, and one
+  // 32-row x 64-byte staging tile per epilogue warp
+  static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES + 256;
+  static constexpr size_t SMEM_BYTES = size_t(EPI_OFF) + 2 * BN * 4 + 8 * 2048 + 1024 /*alignment slack*/;
 };
 
 template <int OUT>
@@ -89,6 +95,11 @@ __device__ __forceinline__ void store_chunk32(void* C, long long off, const floa
   }
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
 __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off, float v) {
   if (out_dtype == kOutF16) reinterpret_cast<__half*>(C)[off] = __float2half_rn(v);
   else if (out_dtype == kOutF32) reinterpret_cast<float*>(C)[off] = v;
@@ -97,7 +108,7 @@ __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off,
 }
 
 template <int BN, int KIND>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const GemmParams p) {
   using Cfg = GemmCfg<BN, KIND>;
@@ -132,7 +143,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);   // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), 8);   // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
@@ -212,23 +223,41 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    const int ew = warp - 2;                // 0..7
     const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
+    const int half = ew >> 2;               // which half of the tile's columns this warp handles
+    constexpr int CPW = BN / 64;            // 32-column chunks per warp
+    const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
+    float* bias_s = reinterpret_cast<float*>(smem + Cfg::EPI_OFF);                  // [2][BN]
+    const uint32_t stage_u = base + Cfg::EPI_OFF + 2 * BN * 4 + ew * 2048;          // 32 rows x 64 B
+    // 16-byte chunk q of staged row r; XOR swizzle keeps both access patterns bank-conflict free
+    auto stage_off = [&](int r, int q) { return stage_u + r * 64 + ((q ^ ((r >> 1) & 3)) << 4); };
+
+    const bool al_c = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && p.ldc % 8 == 0;
+    const bool al_r = p.residual == nullptr ||
+                      ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+    const bool al_b = p.bias == nullptr || ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+    const bool al_cs = p.col_scale == nullptr || ((reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
+    const bool vec_ok = al_c && al_r && al_b && al_cs;
+    // staged path: f16 / e4m3 outputs on aligned buffers (the shapes of the network's hot GEMMs)
+    const bool staged_ok = al_c && al_r && p.col_scale == nullptr && p.out_dtype != kOutF32;
+    bool alive = true;
     int local = 0;
-    const bool vec_c = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    const bool vec_r = p.residual == nullptr ||
-                       ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
-    const bool vec_b = p.bias == nullptr || ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-    const bool vec_cs = p.col_scale == nullptr || ((reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
-    const bool vec_ok = vec_c && vec_r && vec_b && vec_cs;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
       const int as = local & 1;
       const uint32_t aph = (local >> 1) & 1u;
       const int m0 = (t / tiles_n) * BM;
       const int n0 = (t % tiles_n) * BN;
-      if (!mbar_wait(tfull_bar(as), aph)) {
-        if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
-        break;
+      // this tile's bias slice goes to shared memory while the MMAs are still running
+      if (p.bias != nullptr) {
+        for (int e = et; e < BN; e += 256) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
       }
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
+      if (alive && !mbar_wait(tfull_bar(as), aph)) {
+        if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
+        alive = false;           // keep iterating so that the named barrier above stays balanced
+      }
+      if (!alive) continue;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
@@ -236,9 +265,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
       const float a_scale = p.alpha * rs;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int c = half * CPW + cc;
         const int c0 = n0 + c * 32;
         if (c0 >= p.N) break;               // warp-uniform
+        const bool staged = staged_ok && c0 + 32 <= p.N;
+        // residual rows in the coalesced mapping (lane -> row (lane>>2)+8i, 16-byte chunk lane&3),
+        // requested before the accumulator is touched so that the latency overlaps
+        uint4 rres[4];
+        if (staged && p.residual != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int gr = m0 + quarter * 32 + (lane >> 2) + 8 * i;
+            if (gr < p.M) {
+              const int rr = p.res_mod > 0 ? gr % p.res_mod : gr;
+              rres[i] = *reinterpret_cast<const uint4*>(p.residual + (long long)rr * p.ldr + c0 + (lane & 3) * 8);
+            } else {
+              rres[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+        }
         uint32_t acc[32];
         tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(as * BN + c * 32), acc);
         tmem_ld_wait();
@@ -248,7 +294,75 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (KIND == kKindI8) v[j] = static_cast<float>(static_cast<int>(acc[j])) * a_scale;
           else v[j] = __uint_as_float(acc[j]) * a_scale;
         }
-        if (c0 + 32 <= p.N && vec_ok) {
+        if (staged) {
+          if (p.bias != nullptr) {
+            const float4* b4p = reinterpret_cast<const float4*>(bias_s + as * BN + c * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 b4 = b4p[q];
+              v[q * 4] += b4.x; v[q * 4 + 1] += b4.y; v[q * 4 + 2] += b4.z; v[q * 4 + 3] += b4.w;
+            }
+          }
+          // activation: the switch sits outside the element loop so that the 32 independent
+          // evaluations interleave
+          if (p.act == kActMish) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_mish(v[j]);
+          } else if (p.act == kActGelu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = act_gelu(v[j]);
+          } else if (p.act == kActRelu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+          }
+          if (p.out_dtype == kOutE4M3) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
+          }
+          // row-per-thread f16 -> swizzled staging
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t w0 = pack_f16x2(v[q * 8 + 0], v[q * 8 + 1]), w1 = pack_f16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            const uint32_t w2 = pack_f16x2(v[q * 8 + 4], v[q * 8 + 5]), w3 = pack_f16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_off(lane, q)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
+          __syncwarp();
+          // coalesced write-out: each instruction covers 8 rows x 64 contiguous bytes
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rl = (lane >> 2) + 8 * i, q = lane & 3;
+            uint4 u;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(stage_off(rl, q)));
+            const int gr = m0 + quarter * 32 + rl;
+            if (gr < p.M) {
+              const __half2* h = reinterpret_cast<const __half2*>(&u);
+              if (p.out_dtype == kOutF16) {
+                if (p.residual != nullptr) {
+                  const __half2* r = reinterpret_cast<const __half2*>(&rres[i]);
+                  uint32_t o[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 a = __half22float2(h[j]), b = __half22float2(r[j]);
+                    o[j] = pack_f16x2(a.x + b.x, a.y + b.y);
+                  }
+                  u = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.C) + (long long)gr * p.ldc + c0 + q * 8) = u;
+              } else {
+                uint32_t o[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  const float2 a = __half22float2(h[2 * j]), b = __half22float2(h[2 * j + 1]);
+                  o[j] = uint32_t(__nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3)) |
+                         (uint32_t(__nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3)) << 16);
+                }
+                *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(p.C) + (long long)gr * p.ldc + c0 + q * 8) = make_uint2(o[0], o[1]);
+              }
+            }
+          }
+          __syncwarp();   // the staging tile is rewritten by the next chunk
+        } else if (c0 + 32 <= p.N && vec_ok) {
+          // direct path (f32 output, per-column scales): each thread stores its own row segment
           if (p.col_scale != nullptr) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -257,9 +371,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
           if (p.bias != nullptr) {
+            const float4* b4p = reinterpret_cast<const float4*>(bias_s + as * BN + c * 32);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + c0) + q);
+              const float4 b4 = b4p[q];
               v[q * 4] += b4.x; v[q * 4 + 1] += b4.y; v[q * 4 + 2] += b4.z; v[q * 4 + 3] += b4.w;
             }
           }
@@ -300,7 +415,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (col < p.N) {
               float x = v[j];
               if (p.col_scale != nullptr) x *= p.col_scale[col];
-              if (p.bias != nullptr) x += p.bias[col];
+              if (p.bias != nullptr) x += bias_s[as * BN + c * 32 + j];
               x = apply_act(x, p.act);
               if (p.residual != nullptr) x += __half2float(p.residual[(long long)rrow * p.ldr + col]);
               if (p.out_dtype == kOutE4M3) x *= p.out_scale;

@@ -79,7 +79,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (rc != kOk) return rc;
   const int tiles = ((a.p.M + Cfg::BM - 1) / Cfg::BM) * ((a.p.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_tn_kernel<BN, KIND><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, a.p);
+  gemm_tn_kernel<BN, KIND><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, a.p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 

@@ -184,9 +184,14 @@ __device__ __forceinline__ float act_gelu(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 __device__ __forceinline__ float act_mish(float x) {
-  // x * tanh(softplus(x)), softplus with the usual overflow guard
-  float sp = x > 20.0f ? x : log1pf(__expf(x));
-  return x * tanhf(sp);
+  // x * tanh(softplus(x)) with tanh(log(1+e)) = ((1+e)^2 - 1) / ((1+e)^2 + 1) = n / (n + 2),
+  // n = e * (e + 2), e = exp(x): one ex2 and one rcp on the special-function unit, no branches.
+  // The exponent is clamped at 15, where n / (n + 2) already rounds to 1 in fp32.
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fminf(x, 15.0f) * 1.4426950408889634f));
+  const float n = fmaf(e, e, 2.0f * e);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(n + 2.0f));
+  return x * n * r;
 }
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {

@@ -204,3 +204,17 @@ class Engine:
                                                   ctypes.byref(n)), "profile_read")
             out[name] = dict(ms=ms.value, flops=fl.value, bytes=by.value, launches=n.value)
         return out
+
+    def profile_entries(self):
+        """Every recorded launch in order: dict(cat, ms, flops, bytes, m, n, k, kind)."""
+        out, i = [], 0
+        while True:
+            cat, ms, fl, by = ctypes.c_int(), ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+            mnk = (ctypes.c_int * 4)()
+            rc = self.lib.crl_profile_entry(self._h, i, ctypes.byref(cat), ctypes.byref(ms), ctypes.byref(fl),
+                                            ctypes.byref(by), ctypes.byref(mnk))
+            if rc != 0:
+                return out
+            out.append(dict(cat=cat.value, ms=ms.value, flops=fl.value, bytes=by.value, m=mnk[0], n=mnk[1], k=mnk[2],
+                            kind=mnk[3]))
+            i += 1

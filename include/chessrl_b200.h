@@ -130,6 +130,10 @@ int64_t crl_last_launch_count(const crl_handle* h);
  * and returns summed device time, algorithmic FLOPs and algorithmic bytes of that category. */
 int crl_profile(crl_handle* h, int enable);
 int crl_profile_read(crl_handle* h, int category, double* ms, double* flops, double* bytes, int64_t* launches);
+/* The index-th recorded launch (in launch order): its category, device time, algorithmic FLOPs and bytes, and
+ * for GEMMs {M, N, K, kind} in mnk_kind[4] (zeros otherwise). CRL_ERR_INVALID past the last record. */
+int crl_profile_entry(crl_handle* h, int64_t index, int* category, double* ms, double* flops, double* bytes,
+                      int* mnk_kind);
 const char* crl_error_detail(const crl_handle* h);
 const char* crl_strerror(int status);
 
