@@ -8,8 +8,9 @@
 //   warp 1      : MMA issuer    - one thread issues tcgen05.mma (128 x BN x 32-byte-K) with fp32
 //                 (int32 for int8) accumulators in tensor memory; two accumulator buffers so the
 //                 next tile's main loop overlaps this tile's epilogue
-//   warps 2..9  : epilogue      - tcgen05.ld of the accumulator (a warp may read the 32 TMEM lanes
-//                 its rank modulo 4 selects; two warps share a lane quarter and split the columns),
+//   warps 2..17 : epilogue      - tcgen05.ld of the accumulator (a warp may read the 32 TMEM lanes
+//                 its rank modulo 4 selects; four warps share a lane quarter and split the columns;
+//                 the epilogue is latency-bound, so it wants many warps in flight),
 //                 then scale / bias / activation / residual, convert, store
 // All waits are bounded (see ptx.cuh); a wait that runs out records a status code and unwinds.
 #pragma once
@@ -35,25 +36,36 @@ struct GemmParams {
   int act;                 // Act
   float out_scale;         // multiplies the result before an e4m3 store
   int* status;             // device status word
+  int use_tma_store;       // host built a tensor map for C (f16 / e4m3 output, 16-byte aligned pitch)
 };
 
-constexpr int kGemmThreads = 320;   // TMA warp + MMA warp + 8 epilogue warps
+constexpr int kGemmThreads = 576;   // TMA warp + MMA warp + 16 epilogue warps
+constexpr int kEpiWarps = 16;
 
-template <int BN, int KIND>
+// PAIR = 1: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs. Each CTA stages
+// its own 128 rows of A and its own BN/2 rows of W, so a pair moves a third less data from L2 into
+// shared memory per FLOP than two independent CTAs; the leader CTA (cluster rank 0) issues the MMAs
+// for both, each CTA drains the 128 accumulator rows that land in its own tensor memory.
+template <int BN, int KIND, int PAIR = 0>
 struct GemmCfg {
-  static constexpr int BM = 128;
+  static constexpr int BM = 128;           // rows per CTA
+  static constexpr int TM = PAIR ? 256 : 128;  // rows per tile
   static constexpr int ESZ = (KIND == kKindF16) ? 2 : 1;
   static constexpr int BK = 128 / ESZ;   // elements per stage along K: one 128-byte swizzle row
   static constexpr int UK = 32 / ESZ;    // elements per tcgen05.mma along K
   static constexpr uint32_t A_BYTES = BM * 128;
-  static constexpr uint32_t B_BYTES = BN * 128;
+  static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
-  // after the stages: 256 bytes of mbarriers + TMEM slot, the bias table [2][BN] f32, and one
-  // 32-row x 64-byte staging tile per epilogue warp
-  static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES + 256;
-  static constexpr size_t SMEM_BYTES = size_t(EPI_OFF) + 2 * BN * 4 + 8 * 2048 + 1024 /*alignment slack*/;
+  // after the stages: the bias table [2][BN] f32, one 32-row x 64-byte staging tile per epilogue
+  // warp (512-byte aligned: the TMA store swizzles by absolute address bits), then 128 bytes of
+  // mbarriers + TMEM slot
+  static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
+  static constexpr uint32_t BAR_OFF = EPI_OFF + 2 * BN * 4 + kEpiWarps * 2048;
+  static constexpr uint32_t USED_BYTES = BAR_OFF + 128;
+  static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + 896 /*alignment slack*/;
+  static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
 };
 
 template <int OUT>
@@ -107,29 +119,37 @@ __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off,
       static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-template <int BN, int KIND>
+template <int BN, int KIND, int PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const GemmParams p) {
-  using Cfg = GemmCfg<BN, KIND>;
-  constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES;
+               const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using Cfg = GemmCfg<BN, KIND, PAIR>;
+  constexpr int BM = Cfg::BM, TM = Cfg::TM, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  // cluster rank (0 = leader) and the persistent worker this CTA belongs to
+  const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int worker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int num_workers = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;          // swizzled tiles need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t bar0 = base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar0 = base + Cfg::BAR_OFF;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_slot =
-      reinterpret_cast<uint32_t*>(smem + STAGES * Cfg::STAGE_BYTES + 8 * (2 * STAGES + 4));
+      reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 8 * (2 * STAGES + 4));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (base + Cfg::USED_BYTES > raw + Cfg::SMEM_BYTES) {   // dynamic smem less aligned than planned for
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kDevBadSmemAlign);
+    return;
+  }
 
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = (p.M + TM - 1) / TM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
@@ -143,16 +163,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);   // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
     }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::ACC_COLS);
-    tmem_relinquish();
+    tmem_alloc<PAIR>(smem_u32(tmem_slot), Cfg::ACC_COLS);
+    tmem_relinquish<PAIR>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();      // the peer's barriers and tensor memory are ready too
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -162,9 +183,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / tiles_n) * BM;
-        const int n0 = (t % tiles_n) * BN;
+      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+        const int m0 = (t / tiles_n) * TM + rank * BM;                  // this CTA's rows of A
+        const int n0 = (t % tiles_n) * BN + rank * (PAIR ? BN / 2 : 0);  // this CTA's rows of W
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
             atomicCAS(p.status, 0, kDevTimeoutProducer);
@@ -173,9 +194,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
-          mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-          tma_load_2d(a_dst, &tmA, kb * BK, m0, full_bar(s));
-          tma_load_2d(b_dst, &tmB, kb * BK, n0, full_bar(s));
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
+            const uint32_t lead_full = mapa_u32(full_bar(s), 0);
+            if (rank == 0) mbar_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, lead_full);
+            tma_load_2d_pair(b_dst, &tmB, kb * BK, n0, lead_full);
+          } else {
+            mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmA, kb * BK, m0, full_bar(s));
+            tma_load_2d(b_dst, &tmB, kb * BK, n0, full_bar(s));
+          }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -183,14 +212,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc =
-          umma_idesc(BM, BN, KIND == kKindI8 ? 1 : 0, KIND == kKindI8 ? 2 : 1);
+          umma_idesc(TM, BN, KIND == kKindI8 ? 1 : 0, KIND == kKindI8 ? 2 : 1);
       int s = 0;
       uint32_t ph = 0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = worker; t < num_tiles && ok; t += num_workers, ++local) {
         const int as = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
         if (!mbar_wait(tempty_bar(as), aph ^ 1u)) {
@@ -212,22 +241,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // 32 bytes further along K inside the swizzle row: +2 in the 16-byte address field
-            umma<KIND>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma<KIND, PAIR>(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(empty_bar(s));          // frees the stage once these MMAs have read it
+          tc_commit<PAIR>(empty_bar(s));    // frees the stage (in both CTAs) once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        if (ok) tc_commit(tfull_bar(as));   // accumulator complete
+        if (ok) tc_commit<PAIR>(tfull_bar(as));   // accumulator complete
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue warps
-    const int ew = warp - 2;                // 0..7
+    const int ew = warp - 2;                // 0..15
     const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32)
-    const int half = ew >> 2;               // which half of the tile's columns this warp handles
-    constexpr int CPW = BN / 64;            // 32-column chunks per warp
-    const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
+    const int part = ew >> 2;               // this warp takes the 32-column chunks part, part+4, ...
+    const int et = threadIdx.x - 64;        // 0..511 among the epilogue threads
     float* bias_s = reinterpret_cast<float*>(smem + Cfg::EPI_OFF);                  // [2][BN]
     const uint32_t stage_u = base + Cfg::EPI_OFF + 2 * BN * 4 + ew * 2048;          // 32 rows x 64 B
     // 16-byte chunk q of staged row r; XOR swizzle keeps both access patterns bank-conflict free
@@ -240,19 +268,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool al_cs = p.col_scale == nullptr || ((reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
     const bool vec_ok = al_c && al_r && al_b && al_cs;
     // staged path: f16 / e4m3 outputs on aligned buffers (the shapes of the network's hot GEMMs)
-    const bool staged_ok = al_c && al_r && p.col_scale == nullptr && p.out_dtype != kOutF32;
+    const bool staged_ok = p.use_tma_store != 0 && al_r && p.col_scale == nullptr && p.out_dtype != kOutF32;
     bool alive = true;
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+    for (int t = worker; t < num_tiles; t += num_workers, ++local) {
       const int as = local & 1;
       const uint32_t aph = (local >> 1) & 1u;
-      const int m0 = (t / tiles_n) * BM;
+      const int m0 = (t / tiles_n) * TM + rank * BM;   // first row of this CTA's accumulator half
       const int n0 = (t % tiles_n) * BN;
       // this tile's bias slice goes to shared memory while the MMAs are still running
       if (p.bias != nullptr) {
-        for (int e = et; e < BN; e += 256) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
+        for (int e = et; e < BN; e += kEpiWarps * 32) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
+      asm volatile("bar.sync 1, 512;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
       if (alive && !mbar_wait(tfull_bar(as), aph)) {
         if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
         alive = false;           // keep iterating so that the named barrier above stays balanced
@@ -265,8 +293,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
       const float a_scale = p.alpha * rs;
 #pragma unroll 1
-      for (int cc = 0; cc < CPW; ++cc) {
-        const int c = half * CPW + cc;
+      for (int c = part; c < BN / 32; c += 4) {
         const int c0 = n0 + c * 32;
         if (c0 >= p.N) break;               // warp-uniform
         const bool staged = staged_ok && c0 + 32 <= p.N;
@@ -319,48 +346,62 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
           }
-          // row-per-thread f16 -> swizzled staging
+          if (p.residual != nullptr) {
+            // transpose the coalesced residual rows through the staging tile into row-per-thread order
+            if (lane == 0) bulk_wait_read0();   // the previous chunk's TMA store has read the tile
+            __syncwarp();
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t w0 = pack_f16x2(v[q * 8 + 0], v[q * 8 + 1]), w1 = pack_f16x2(v[q * 8 + 2], v[q * 8 + 3]);
-            const uint32_t w2 = pack_f16x2(v[q * 8 + 4], v[q * 8 + 5]), w3 = pack_f16x2(v[q * 8 + 6], v[q * 8 + 7]);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_off(lane, q)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-          }
-          __syncwarp();
-          // coalesced write-out: each instruction covers 8 rows x 64 contiguous bytes
+            for (int i = 0; i < 4; ++i)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_off((lane >> 2) + 8 * i, lane & 3)),
+                           "r"(rres[i].x), "r"(rres[i].y), "r"(rres[i].z), "r"(rres[i].w) : "memory");
+            __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rl = (lane >> 2) + 8 * i, q = lane & 3;
-            uint4 u;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(stage_off(rl, q)));
-            const int gr = m0 + quarter * 32 + rl;
-            if (gr < p.M) {
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(stage_off(lane, q)));
               const __half2* h = reinterpret_cast<const __half2*>(&u);
-              if (p.out_dtype == kOutF16) {
-                if (p.residual != nullptr) {
-                  const __half2* r = reinterpret_cast<const __half2*>(&rres[i]);
-                  uint32_t o[4];
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 a = __half22float2(h[j]), b = __half22float2(r[j]);
-                    o[j] = pack_f16x2(a.x + b.x, a.y + b.y);
-                  }
-                  u = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.C) + (long long)gr * p.ldc + c0 + q * 8) = u;
-              } else {
-                uint32_t o[2];
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                  const float2 a = __half22float2(h[2 * j]), b = __half22float2(h[2 * j + 1]);
-                  o[j] = uint32_t(__nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3)) |
-                         (uint32_t(__nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3)) << 16);
-                }
-                *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(p.C) + (long long)gr * p.ldc + c0 + q * 8) = make_uint2(o[0], o[1]);
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                v[q * 8 + 2 * j] += f.x;
+                v[q * 8 + 2 * j + 1] += f.y;
               }
             }
+            __syncwarp();
+          } else {
+            if (lane == 0) bulk_wait_read0();
+            __syncwarp();
           }
-          __syncwarp();   // the staging tile is rewritten by the next chunk
+          // row-per-thread results -> swizzled staging tile (the layout a TMA box with the 64-byte,
+          // for e4m3 32-byte, swizzle expects) -> one TMA store per warp and chunk; rows and columns
+          // beyond the matrix are clipped by the TMA unit
+          if (p.out_dtype == kOutF16) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t w0 = pack_f16x2(v[q * 8 + 0], v[q * 8 + 1]), w1 = pack_f16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              const uint32_t w2 = pack_f16x2(v[q * 8 + 4], v[q * 8 + 5]), w3 = pack_f16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_off(lane, q)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float* e = &v[q * 16 + j * 4];
+                w[j] = uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[0], e[1]), __NV_SATFINITE, __NV_E4M3)) |
+                       (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[2], e[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
+              }
+              const uint32_t off8 = stage_u + lane * 32 + ((q ^ ((lane >> 2) & 1)) << 4);   // 32-byte swizzle
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, stage_u, c0, m0 + quarter * 32);
+            bulk_commit();
+          }
         } else if (c0 + 32 <= p.N && vec_ok) {
           // direct path (f32 output, per-column scales): each thread stores its own row segment
           if (p.col_scale != nullptr) {
@@ -427,16 +468,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(as));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
+        else mbar_arrive(tempty_bar(as));
+      }
     }
+    if (lane == 0) bulk_wait_all();   // this warp's TMA stores have left shared memory and landed
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();      // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::ACC_COLS);
+    tmem_dealloc<PAIR>(tmem_base, Cfg::ACC_COLS);
   }
 }
 

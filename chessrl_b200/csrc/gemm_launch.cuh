@@ -3,6 +3,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include "gemm.cuh"
 
@@ -35,19 +37,22 @@ inline PFN_cuTensorMapEncodeTiled_v12000 tmap_encoder() {
 
 // 2-D row-major tensor [outer, inner] with a row pitch in bytes; box = 128 bytes x box_outer rows,
 // 128-byte swizzle, out-of-range elements read as zero.
+// box_bytes is the box's inner extent and selects the swizzle: 128 (operand tiles), 64 or 32 (the
+// epilogue's staging tiles).
 inline int make_tmap_2d(CUtensorMap* out, const void* ptr, int esz, uint64_t inner, uint64_t outer,
-                        uint64_t pitch_bytes, uint32_t box_outer) {
+                        uint64_t pitch_bytes, uint32_t box_outer, uint32_t box_bytes = 128) {
   auto enc = tmap_encoder();
   if (enc == nullptr) return kErrCuda;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (pitch_bytes & 15) != 0) return kErrShape;
   cuuint64_t gdim[2] = {inner, outer};
   cuuint64_t gstride[1] = {pitch_bytes};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), box_outer};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes / esz), box_outer};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : (box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   CUresult r = enc(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
-                   const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kOk : kErrCuda;
 }
 
@@ -60,14 +65,14 @@ struct GemmArgs {
   GemmParams p{};
 };
 
-template <int BN, int KIND>
+template <int BN, int KIND, int PAIR = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, KIND>;
+  using Cfg = GemmCfg<BN, KIND, PAIR>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -75,12 +80,38 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, a.A, Cfg::ESZ, a.p.K, a.p.M, a.lda * Cfg::ESZ, Cfg::BM);
   if (rc != kOk) return rc;
-  rc = make_tmap_2d(&tmB, a.W, Cfg::ESZ, a.p.K, a.p.N, a.ldw * Cfg::ESZ, BN);
+  rc = make_tmap_2d(&tmB, a.W, Cfg::ESZ, a.p.K, a.p.N, a.ldw * Cfg::ESZ, PAIR ? BN / 2 : BN);
   if (rc != kOk) return rc;
-  const int tiles = ((a.p.M + Cfg::BM - 1) / Cfg::BM) * ((a.p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_tn_kernel<BN, KIND><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, a.p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+  // output tensor map for the epilogue's TMA stores: 32 rows x 32 columns per box
+  CUtensorMap tmC;
+  GemmParams prm = a.p;
+  prm.use_tma_store = 0;
+  std::memset(&tmC, 0, sizeof(tmC));
+  if (prm.out_dtype != kOutF32) {
+    const int oesz = prm.out_dtype == kOutF16 ? 2 : 1;
+    if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, 32 * oesz) == kOk)
+      prm.use_tma_store = 1;
+  }
+  const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
+  if constexpr (PAIR) {
+    // one 2-CTA cluster per pair of SMs
+    const int pairs = tiles < num_sms / 2 ? tiles : num_sms / 2;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR>, tmA, tmB, tmC, prm) == cudaSuccess ? kOk : kErrCuda;
+  } else {
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    gemm_tn_kernel<BN, KIND, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, prm);
+    return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+  }
 }
 
 template <int KIND>
@@ -90,6 +121,10 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (a.p.N <= 64) bn = 64;
   else if (a.p.N <= 128) bn = 128;
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
+  // large problems: CTA pairs on 256 x 256 tiles (CRL_GEMM_PAIR=0 turns them off for comparisons)
+  static const bool pair_ok = [] { const char* e = getenv("CRL_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+  if (pair_ok && a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2)
+    return gemm_launch_t<256, KIND, 1>(a, num_sms, stream);
   if (bn == 64) return gemm_launch_t<64, KIND>(a, num_sms, stream);
   if (bn == 128) return gemm_launch_t<128, KIND>(a, num_sms, stream);
   return gemm_launch_t<256, KIND>(a, num_sms, stream);

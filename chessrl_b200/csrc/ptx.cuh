@@ -19,6 +19,7 @@ enum DeviceStatus : int {
   kDevTimeoutProducer = 101,   // TMA producer never saw a free stage
   kDevTimeoutMma = 102,        // MMA issuer never saw a filled stage / free accumulator
   kDevTimeoutEpilogue = 103,   // epilogue never saw a finished accumulator
+  kDevBadSmemAlign = 104,      // dynamic shared memory base less aligned than the layout allows for
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -68,6 +69,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// 2-CTA clusters
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// cluster-window address of this CTA's shared-memory address `addr` in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // TMA: 2-D tiled load global -> shared (this CTA only), completion on an mbarrier
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
@@ -81,20 +104,54 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
       : "memory");
 }
 
+// Same load into this CTA's shared memory, but the bytes are counted on an mbarrier given by its
+// cluster-window address (the leader CTA's barrier when a CTA pair feeds one cta_group::2 MMA).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+
+// 2-D tiled store shared -> global (bulk async-group completion). Elements outside the tensor are
+// not written. Generic-proxy writes to the source tile need fence_proxy_async_smem() + a barrier first.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all earlier bulk groups of this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed entirely
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory + MMA
 // ---------------------------------------------------------------------------------------------
+// PAIR = 1 variants act on both CTAs of a 2-CTA cluster (cta_group::2): the same warp of each CTA
+// executes them with the same operands.
+template <int PAIR = 0>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
-               "r"(ncols)
-               : "memory");
+  if constexpr (PAIR)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
 }
+template <int PAIR = 0>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (PAIR) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+template <int PAIR = 0>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
+  if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -103,10 +160,16 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 // The mbarrier gets one arrival once every MMA issued so far by this thread has finished.
+// PAIR = 1: issued by the leader CTA; the same barrier (same shared-memory offset) of both CTAs gets
+// its arrival, through two plain commits to the two cluster-window addresses.
+template <int PAIR = 0>
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
+  if constexpr (PAIR) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mapa_u32(bar, 0)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mapa_u32(bar, 1)) : "memory");
+  } else {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  }
 }
 
 // Shared-memory matrix descriptor for a K-major tile stored with the 128-byte swizzle (the layout
@@ -133,29 +196,27 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int fmt_ab, int 
 
 enum MmaKind : int { kKindF16 = 0, kKindF8 = 1, kKindI8 = 2 };
 
-template <int KIND>
+#define CRL_UMMA_ASM(GROUP, KINDSTR)                                                              \
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                   \
+               "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t}\n" ::"r"( \
+                   tmem_d),                                                                       \
+               "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)                              \
+               : "memory")
+
+// D[tmem] (+)= A[smem] * B[smem]^T. PAIR = 1: one instruction drives the tensor cores of both CTAs
+// (M = 256: rows 0..127 accumulate in the leader's tensor memory, 128..255 in the peer's).
+template <int KIND, int PAIR = 0>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                      uint32_t idesc, uint32_t accumulate) {
   if constexpr (KIND == kKindF16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) CRL_UMMA_ASM("2", "f16"); else CRL_UMMA_ASM("1", "f16");
   } else if constexpr (KIND == kKindF8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) CRL_UMMA_ASM("2", "f8f6f4"); else CRL_UMMA_ASM("1", "f8f6f4");
   } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) CRL_UMMA_ASM("2", "i8"); else CRL_UMMA_ASM("1", "i8");
   }
 }
+#undef CRL_UMMA_ASM
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives row (lane base + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -20,7 +20,7 @@ def call(lib, kind, a, w, out_dtype, bias=None, res=None, alpha=1.0, act=0):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (64, 32, 1024), (200, 1929, 4096), (320, 256, 112), (1, 128, 8192),
-                                   (4096, 3072, 1024), (777, 1536, 1024), (130, 8200, 256)])
+                                   (4096, 3072, 1024), (777, 1536, 1024), (130, 8200, 256), (19001, 520, 200), (9473, 1929, 512)])
 def test_f16_gemm(lib, m, n, k):
     torch.manual_seed(m + n + k)
     a = torch.randn(m, k, device="cuda").half()
