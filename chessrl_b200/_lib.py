@@ -25,7 +25,7 @@ EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
-    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry",
+    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static",
 ]
 
 
@@ -84,6 +84,8 @@ def load():
     lib.crl_forward.restype = ctypes.c_int
     lib.crl_forward_host.argtypes = [vp, ctypes.POINTER(IO)]
     lib.crl_forward_host.restype = ctypes.c_int
+    lib.crl_forward_static.argtypes = [vp, ctypes.POINTER(IO)]
+    lib.crl_forward_static.restype = ctypes.c_int
     lib.crl_last_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
     lib.crl_last_status.restype = ctypes.c_int
     lib.crl_last_launch_count.argtypes = [vp]

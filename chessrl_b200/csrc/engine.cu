@@ -921,6 +921,36 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
   return CRL_OK;
 }
 
+// Scratch for crl_forward_static: lives in the library's device image, so no allocation call is ever
+// needed for it. Every GPU that loads the library carries these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[CRL_STATIC_SCRATCH_BYTES];
+// Device address of g_static_scratch per device (the name above is only a host-side stand-in for the
+// symbol; kernels must be given the address cudaGetSymbolAddress reports for the current device).
+static void* g_static_scratch_addr[64] = {};
+
+int crl_forward_static(crl_handle* h, const crl_io* io) {
+  int rc = check_io(h, io);
+  if (rc != CRL_OK) return rc;
+  if (h->device < 0 || h->device >= 64) return fail(h, CRL_ERR_UNSUPPORTED, "device index beyond the static scratch table");
+  const size_t need = crl_workspace_bytes(h, io->batch);
+  if (need > static_cast<size_t>(CRL_STATIC_SCRATCH_BYTES))
+    return fail(h, CRL_ERR_WORKSPACE, "batch " + std::to_string(io->batch) + " needs " + std::to_string(need) +
+                                          " bytes of scratch; the static scratch of crl_forward_static holds " +
+                                          std::to_string(static_cast<size_t>(CRL_STATIC_SCRATCH_BYTES)));
+  CRL_CUDA(h, cudaSetDevice(h->device));
+  if (g_static_scratch_addr[h->device] == nullptr) {
+    // one-time set-up per device, with that device current
+    void* ptr = nullptr;
+    CRL_CUDA(h, cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_addr[h->device] = ptr;
+  }
+  crl_io with_scratch = *io;
+  with_scratch.workspace = g_static_scratch_addr[h->device];
+  with_scratch.workspace_bytes = static_cast<size_t>(CRL_STATIC_SCRATCH_BYTES);
+  h->launches = 0;
+  return run_batch(h, &with_scratch, false);
+}
+
 int crl_last_status(crl_handle* h, int* device_status_word) {
   if (h == nullptr || device_status_word == nullptr) return CRL_ERR_INVALID;
   CRL_CUDA(h, cudaSetDevice(h->device));

@@ -118,6 +118,26 @@ int crl_forward(crl_handle* h, const crl_io* io);
  * synchronises. Staging buffers and workspace are owned by the handle and grow on demand. */
 int crl_forward_host(crl_handle* h, const crl_io* io);
 
+/* crl_forward for callers that must not allocate device memory (no counterpart in the reference, which
+ * leaves all memory management to PyTorch). Think of a search or serving thread that runs beside a
+ * framework which has already reserved the GPU's memory for its own caching allocator, or of a
+ * latency-critical loop in which the device-wide synchronisation hidden in cudaMalloc / cudaFree would
+ * stall every other stream: such a caller passes device pointers for planes, mask and outputs as usual and
+ * leaves io->workspace unset; the scratch comes from a CRL_STATIC_SCRATCH_BYTES array inside the
+ * library's device image (each GPU that loads the library holds it until the process exits). The call
+ * itself makes no cudaMalloc / cudaFree and uses no allocating library.
+ *   - Limit: crl_workspace_bytes(h, io->batch) must not exceed CRL_STATIC_SCRATCH_BYTES (a few dozen
+ *     positions of a 1024-wide network, a few hundred of a 256-wide one); larger batches are refused with
+ *     CRL_ERR_WORKSPACE and crl_error_detail() says how many bytes were needed.
+ *   - The first call on each device looks up the array's device address; make that first call outside
+ *     any stream capture.
+ *   - All calls (all handles on a device) share the one array, and it keeps what the last call left in
+ *     it. The forward pass writes every scratch buffer before reading it, so nothing needs clearing, but
+ *     two calls whose kernels overlap on the GPU (different streams, different handles) race on it:
+ *     serialise them. */
+#define CRL_STATIC_SCRATCH_BYTES (64u << 20)
+int crl_forward_static(crl_handle* h, const crl_io* io);
+
 /* Reads and clears the device status word (0 = fine, 101/102/103 = a bounded wait of the GEMM's
  * producer / MMA / epilogue role ran out). Synchronises the device. */
 int crl_last_status(crl_handle* h, int* device_status_word);
