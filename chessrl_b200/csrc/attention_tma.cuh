@@ -1,0 +1,224 @@
+// Pipelined per-board attention for head_dim 32 (the widths the engine is benchmarked at): the same
+// math as attention.cuh, restructured so that HBM latency is hidden. Persistent CTAs, one per SM; every
+// warp runs its own two-stage pipeline over (board, head) items: one lane issues TMA box loads of the
+// Q, K, V tiles (64 x 64 bytes each, 64-byte swizzle) and of the 64 x 64 smolgen bias tile (f16 or
+// e4m3) for item i+1 while the warp computes item i; the context tile goes back through a swizzled
+// staging tile and a TMA store. Completion is tracked by per-warp mbarriers; waits are bounded.
+#pragma once
+#include <cuda.h>
+#include "attention.cuh"
+
+namespace crl {
+
+// NW warps per CTA: 14 when the bias tile is e4m3 or absent (16 KB per warp), 11 with an f16 bias tile
+// (20 KB per warp). The kernel is latency-bound per warp (dependent ldmatrix / mma / exp chains), so it
+// wants as many warps per SM as shared memory allows rather than deep per-warp buffering; two 16-row
+// query slabs are processed together for instruction-level parallelism.
+struct AttnTmaParams {
+  int B, H;
+  float scale;
+  int has_bias;          // 0 none, 1 f16 tile, 2 e4m3 tile
+  float bias_mult;       // e4m3 bias: value = byte * bias_mult
+  int out_e4m3;          // 0: f16 context, 1: e4m3 (scaled by out_scale)
+  float out_scale;
+  int d;
+  int* status;
+};
+
+template <int NW>
+struct AttnTmaSmem {
+  static constexpr int PER_WARP = (NW > 11 ? 16 : 20) * 1024;   // Q/out 4K | K 4K | V 4K | bias 4K or 8K
+  static constexpr int BAR_OFF = NW * PER_WARP;
+  static constexpr int BYTES = BAR_OFF + NW * 8 + 1024;
+};
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmBias,
+                     const __grid_constant__ CUtensorMap tmOut, const AttnTmaParams p) {
+  using SM = AttnTmaSmem<NW>;
+  extern __shared__ uint8_t smem_at_raw[];
+  const uint32_t raw = smem_u32(smem_at_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t wbase = base + warp * SM::PER_WARP;
+  const uint32_t bar = base + SM::BAR_OFF + warp * 8;
+  const uint8_t* sB = smem_at_raw + (base - raw) + warp * SM::PER_WARP + 12288;
+  const uint32_t sQ = wbase, sK = wbase + 4096, sV = wbase + 8192;
+  const uint32_t out_u = wbase;          // the context tile overlays the Q tile, slab by slab
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (warp == 0) { tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmBias); tma_prefetch_desc(&tmOut); }
+  }
+  __syncwarp();
+
+  const long long items = (long long)p.B * p.H;
+  const long long first = (long long)blockIdx.x * NW + warp;
+  const long long stride = (long long)gridDim.x * NW;
+  const uint32_t stage_bytes = 3u * 4096u + (p.has_bias == 1 ? 8192u : (p.has_bias == 2 ? 4096u : 0u));
+  const int g = lane >> 2, t = lane & 3;
+  int it = 0;
+  for (long long item = first; item < items; item += stride, ++it) {
+    const int board = static_cast<int>(item / p.H), h = static_cast<int>(item % p.H);
+    if (lane == 0) {
+      bulk_wait_read0();                 // the previous context tile has been read out of the Q region
+      mbar_expect_tx(bar, stage_bytes);
+      tma_load_2d(sQ, &tmQKV, h * 32, board * 64, bar);
+      tma_load_2d(sK, &tmQKV, p.d + h * 32, board * 64, bar);
+      tma_load_2d(sV, &tmQKV, 2 * p.d + h * 32, board * 64, bar);
+      if (p.has_bias) tma_load_2d(wbase + 12288, &tmBias, 0, static_cast<int>(item * 64), bar);
+    }
+    if (!mbar_wait(bar, it & 1)) {
+      if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue + 10);
+      break;
+    }
+
+    for (int half = 0; half < 2; ++half) {
+      float s[2][8][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[u][n][0] = s[u][n][1] = s[u][n][2] = s[u][n][3] = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          ldsm_x4(sQ + tile_off<32>((half * 2 + u) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)),
+                  a[u][0], a[u][1], a[u][2], a[u][3]);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(sK + tile_off<32>(np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            mma16816(s[u][2 * np], a[u][0], a[u][1], a[u][2], a[u][3], b0, b1);
+            mma16816(s[u][2 * np + 1], a[u][0], a[u][1], a[u][2], a[u][3], b2, b3);
+          }
+        }
+      }
+      float inv[2][2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r0 = (half * 2 + u) * 16 + g;
+        if (p.has_bias == 1) {
+          // f16 tile, 128-byte rows, 128-byte swizzle: 16-byte chunk n of row r sits at chunk n ^ (r & 7)
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+            const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(sB + r0 * 128 + ((n ^ (r0 & 7)) << 4) + 4 * t));
+            const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(sB + (r0 + 8) * 128 + ((n ^ ((r0 + 8) & 7)) << 4) + 4 * t));
+            s[u][n][0] = s[u][n][0] * p.scale + b0.x; s[u][n][1] = s[u][n][1] * p.scale + b0.y;
+            s[u][n][2] = s[u][n][2] * p.scale + b1.x; s[u][n][3] = s[u][n][3] * p.scale + b1.y;
+          }
+        } else if (p.has_bias == 2) {
+          // e4m3 tile, 64-byte rows, 64-byte swizzle
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+            const int ra = r0, rb = r0 + 8;
+            const uint16_t wa = *reinterpret_cast<const uint16_t*>(sB + ra * 64 + (((n >> 1) ^ ((ra >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
+            const uint16_t wb = *reinterpret_cast<const uint16_t*>(sB + rb * 64 + (((n >> 1) ^ ((rb >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
+            const __half2_raw ha = __nv_cvt_fp8x2_to_halfraw2(wa, __NV_E4M3), hb = __nv_cvt_fp8x2_to_halfraw2(wb, __NV_E4M3);
+            const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ha));
+            const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&hb));
+            s[u][n][0] = s[u][n][0] * p.scale + b0.x * p.bias_mult; s[u][n][1] = s[u][n][1] * p.scale + b0.y * p.bias_mult;
+            s[u][n][2] = s[u][n][2] * p.scale + b1.x * p.bias_mult; s[u][n][3] = s[u][n][3] * p.scale + b1.y * p.bias_mult;
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[u][n][j] *= p.scale;
+          }
+        }
+        float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          m0 = fmaxf(m0, fmaxf(s[u][n][0], s[u][n][1]));
+          m1 = fmaxf(m1, fmaxf(s[u][n][2], s[u][n][3]));
+        }
+        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+        float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          s[u][n][0] = __expf(s[u][n][0] - m0); s[u][n][1] = __expf(s[u][n][1] - m0);
+          s[u][n][2] = __expf(s[u][n][2] - m1); s[u][n][3] = __expf(s[u][n][3] - m1);
+          l0 += s[u][n][0] + s[u][n][1];
+          l1 += s[u][n][2] + s[u][n][3];
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        inv[u][0] = 1.0f / l0; inv[u][1] = 1.0f / l1;
+      }
+      float o[2][4][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int n = 0; n < 4; ++n) o[u][n][0] = o[u][n][1] = o[u][n][2] = o[u][n][3] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          a[u][0] = pack_h2(s[u][2 * kk][0], s[u][2 * kk][1]);
+          a[u][1] = pack_h2(s[u][2 * kk][2], s[u][2 * kk][3]);
+          a[u][2] = pack_h2(s[u][2 * kk + 1][0], s[u][2 * kk + 1][1]);
+          a[u][3] = pack_h2(s[u][2 * kk + 1][2], s[u][2 * kk + 1][3]);
+        }
+#pragma unroll
+        for (int dp = 0; dp < 2; ++dp) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(sV + tile_off<32>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + ((lane >> 4) & 1)), b0, b1, b2, b3);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            mma16816(o[u][2 * dp], a[u][0], a[u][1], a[u][2], a[u][3], b0, b1);
+            mma16816(o[u][2 * dp + 1], a[u][0], a[u][1], a[u][2], a[u][3], b2, b3);
+          }
+        }
+      }
+      // Every lane has taken its Q fragments of these two slabs: their rows now receive the context,
+      // in the layout the store's tensor map swizzles.
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r0 = (half * 2 + u) * 16 + g;
+        float inv0 = inv[u][0], inv1 = inv[u][1];
+        if (p.out_e4m3) {
+          inv0 *= p.out_scale; inv1 *= p.out_scale;
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            const uint16_t w0 = __nv_cvt_float2_to_fp8x2(make_float2(o[u][n][0] * inv0, o[u][n][1] * inv0), __NV_SATFINITE, __NV_E4M3);
+            const uint16_t w1 = __nv_cvt_float2_to_fp8x2(make_float2(o[u][n][2] * inv1, o[u][n][3] * inv1), __NV_SATFINITE, __NV_E4M3);
+            const int ra = r0, rb = r0 + 8;   // 32-byte rows, 32-byte swizzle: chunk (n>>1) ^ ((r>>2)&1)
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_u + ra * 32 + (((n >> 1) ^ ((ra >> 2) & 1)) << 4) + (n & 1) * 8 + 2 * t), "h"(w0) : "memory");
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_u + rb * 32 + (((n >> 1) ^ ((rb >> 2) & 1)) << 4) + (n & 1) * 8 + 2 * t), "h"(w1) : "memory");
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            const uint32_t w0 = pack_h2(o[u][n][0] * inv0, o[u][n][1] * inv0), w1 = pack_h2(o[u][n][2] * inv1, o[u][n][3] * inv1);
+            const int ra = r0, rb = r0 + 8;   // 64-byte rows, 64-byte swizzle
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(out_u + ra * 64 + ((n ^ ((ra >> 1) & 3)) << 4) + 4 * t), "r"(w0) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(out_u + rb * 64 + ((n ^ ((rb >> 1) & 3)) << 4) + 4 * t), "r"(w1) : "memory");
+          }
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();     // context tile complete, and every lane is done with K, V and the bias tile
+    if (lane == 0) {
+      tma_store_2d(&tmOut, out_u, h * 32, board * 64);
+      bulk_commit();
+    }
+  }
+  if (lane == 0) bulk_wait_all();
+  __syncwarp();
+}
+
+}  // namespace crl

@@ -12,6 +12,7 @@
 
 #include "../../include/chessrl_b200.h"
 #include "attention.cuh"
+#include "attention_tma.cuh"
 #include "gemm_launch.cuh"
 #include "policy.cuh"
 #include "rows.cuh"
@@ -32,7 +33,7 @@ struct LayerW {
   // FP8: e4m3 weights, the multipliers they were quantised with, and the activation multipliers
   uint8_t *wqkv8 = nullptr, *wo8 = nullptr, *wff1_8 = nullptr, *wff2_8 = nullptr;
   float sw_qkv = 1, sw_o = 1, sw_ff1 = 1, sw_ff2 = 1;
-  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1;
+  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1;
 };
 
 struct ValueW {
@@ -58,7 +59,7 @@ struct crl_handle {
   std::vector<void*> allocs;
   std::string detail;
   int* status_dev = nullptr;
-  unsigned int* amax_dev = nullptr;   // [L*4] float bit patterns
+  unsigned int* amax_dev = nullptr;   // [L*8] float bit patterns (5 taps per layer used)
   int64_t launches = 0;
   // optional per-kernel timing (crl_profile): event pairs around every launch, by category
   struct ProfRec { cudaEvent_t a, b; int cat; double flops, bytes; int m, n, k, kind; };
@@ -305,6 +306,35 @@ int tap_amax(crl_handle* h, const __half* x, long long rows, int cols, int slot,
   return CRL_OK;
 }
 
+template <int NW>
+int attention_tma_launch_t(crl_handle* h, const AttnTmaParams& t, const CUtensorMap& tq, const CUtensorMap& tb,
+                           const CUtensorMap& to, cudaStream_t s) {
+  static bool attr_set[64] = {};
+  if (h->device >= 0 && h->device < 64 && !attr_set[h->device]) {
+    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTmaSmem<NW>::BYTES));
+    attr_set[h->device] = true;
+  }
+  const long long items = static_cast<long long>(t.B) * t.H;
+  const long long want = (items + NW - 1) / NW;
+  const unsigned grid = static_cast<unsigned>(want < h->num_sms ? want : h->num_sms);
+  attention_tma_kernel<NW><<<grid, NW * 32, AttnTmaSmem<NW>::BYTES, s>>>(tq, tb, to, t);
+  CRL_CUDA(h, cudaGetLastError());
+  return CRL_OK;
+}
+
+int attention_tma_launch(crl_handle* h, const AttnTmaParams& t, const __half* qkv, const void* bias, void* out,
+                         cudaStream_t s) {
+  const uint64_t M = static_cast<uint64_t>(t.B) * 64;
+  CUtensorMap tq, tb, to;
+  std::memset(&tb, 0, sizeof(tb));
+  int rc = make_tmap_2d(&tq, qkv, 2, 3ull * t.d, M, 3ull * t.d * 2, 64, 64);
+  if (rc == kOk && t.has_bias == 1) rc = make_tmap_2d(&tb, bias, 2, 64, static_cast<uint64_t>(t.B) * t.H * 64, 128, 64, 128);
+  if (rc == kOk && t.has_bias == 2) rc = make_tmap_2d(&tb, bias, 1, 64, static_cast<uint64_t>(t.B) * t.H * 64, 64, 64, 64);
+  if (rc == kOk) rc = t.out_e4m3 ? make_tmap_2d(&to, out, 1, t.d, M, t.d, 64, 32) : make_tmap_2d(&to, out, 2, t.d, M, 2ull * t.d, 64, 64);
+  if (rc != kOk) return fail(h, rc, "attention: tensor map encoding failed");
+  return t.has_bias == 1 ? attention_tma_launch_t<11>(h, t, tq, tb, to, s) : attention_tma_launch_t<14>(h, t, tq, tb, to, s);
+}
+
 int act_of(const crl_config& c) { return c.act == CRL_ACT_MISH ? kActMish : kActGelu; }
 
 int value_head(crl_handle* h, const ValueW& vw, const __half* x, __half* v1, __half* v2, int64_t bc, float* out,
@@ -377,7 +407,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
         return rc;
       attn_in = w.xn;
     }
-    if (calib && (rc = tap_amax(h, attn_in, M, d, l * 4 + 0, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_amax(h, attn_in, M, d, l * 8 + 0, s)) != CRL_OK) return rc;
     // QKV projection (attn.py:501-503 fused into one [3d, d] weight)
     {
       Lin q; q.m = M; q.n = 3 * d; q.k = d; q.c = w.t1; q.ldc = 3 * d; q.bias = L.bqkv;
@@ -400,7 +430,9 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if ((rc = layer_norm(h, w.sg_h2, bc * H, gen, L.sg_ln2w, L.sg_ln2b, w.sg_h2n, nullptr, 1.0f, nullptr, nullptr, s)) != CRL_OK) return rc;
       Lin f; f.a = w.sg_h2n; f.lda = gen; f.w = h->sg_shared; f.ldw = gen; f.c = w.sg_bias; f.ldc = 4096; f.m = bc * H; f.n = 4096;
       f.k = gen;
+      if (f8) { f.out = kOutE4M3; f.out_scale = L.sa_bias; }   // the bias tile crosses HBM as e4m3
       if ((rc = linear(h, f, s)) != CRL_OK) return rc;
+      if (calib && (rc = tap_amax(h, w.sg_bias, bc * H, 4096, l * 8 + 4, s)) != CRL_OK) return rc;
     }
     // fused attention
     {
@@ -413,11 +445,21 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       else { a.out = w.t2; a.out8 = nullptr; a.out8_scale = 1.0f; }
       ProfScope ps(h, s, kCatAttention, 4.0 * M * 64 * d,
                    static_cast<double>(M) * d * 2 * 3 + static_cast<double>(M) * d * (f8 ? 1 : 2) +
-                       (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * 8192 : 0.0));
-      CRL_CUDA(h, attention_launch(a, h->hd, c.bias_mode, s));
+                       (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * (f8 ? 4096 : 8192) : 0.0));
+      if (h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN)) {
+        AttnTmaParams t{};
+        t.B = static_cast<int>(bc); t.H = H; t.scale = a.scale; t.d = d; t.status = h->status_dev;
+        t.has_bias = c.bias_mode == CRL_BIAS_SMOLGEN ? (f8 ? 2 : 1) : 0;
+        t.bias_mult = f8 ? 1.0f / L.sa_bias : 1.0f;
+        t.out_e4m3 = f8 ? 1 : 0; t.out_scale = f8 ? L.sa_ctx : 1.0f;
+        if ((rc = attention_tma_launch(h, t, w.t1, w.sg_bias, f8 ? static_cast<void*>(w.t2_8) : static_cast<void*>(w.t2), s)) != CRL_OK)
+          return rc;
+      } else {
+        CRL_CUDA(h, attention_launch(a, h->hd, c.bias_mode, s));
+      }
       ++h->launches;
     }
-    if (calib && (rc = tap_amax(h, w.t2, M, d, l * 4 + 1, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_amax(h, w.t2, M, d, l * 8 + 1, s)) != CRL_OK) return rc;
     // out-proj + residual (+ LayerNorm for post-LN)
     {
       Lin o; o.m = M; o.n = d; o.k = d; o.bias = L.bo; o.res = w.x; o.ldr = d; o.lda = d; o.ldw = d;
@@ -434,7 +476,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if ((rc = layer_norm(h, w.x, M, d, L.ln2w, L.ln2b, w.xn, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s)) != CRL_OK) return rc;
       ffn_in = w.xn;
     }
-    if (calib && (rc = tap_amax(h, ffn_in, M, d, l * 4 + 2, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_amax(h, ffn_in, M, d, l * 8 + 2, s)) != CRL_OK) return rc;
     // FFN (value.py:65-67: act after ff2; specification: act between)
     {
       Lin a; a.m = M; a.n = ff; a.k = d; a.bias = L.bff1; a.lda = d; a.ldw = d; a.ldc = ff;
@@ -442,7 +484,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if (f8) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; }
       else { a.a = ffn_in; a.w = L.wff1; a.c = w.t1; }
       if ((rc = linear(h, a, s)) != CRL_OK) return rc;
-      if (calib && (rc = tap_amax(h, w.t1, M, ff, l * 4 + 3, s)) != CRL_OK) return rc;
+      if (calib && (rc = tap_amax(h, w.t1, M, ff, l * 8 + 3, s)) != CRL_OK) return rc;
       Lin b; b.m = M; b.n = d; b.k = ff; b.bias = L.bff2; b.lda = ff; b.ldw = ff; b.res = w.x; b.ldr = d;
       b.act = c.ffn_act_pos == CRL_FFN_ACT_END ? act : kActNone;
       b.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; b.ldc = d;
@@ -634,7 +676,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
   h->status_dev = static_cast<int*>(p);
   cudaMemset(p, 0, 16);
   h->allocs.push_back(p);
-  if (cudaMalloc(&p, sizeof(unsigned int) * 4 * c.n_layers) != cudaSuccess) { crl_destroy(h); return CRL_ERR_CUDA; }
+  if (cudaMalloc(&p, sizeof(unsigned int) * 8 * c.n_layers) != cudaSuccess) { crl_destroy(h); return CRL_ERR_CUDA; }
   h->amax_dev = static_cast<unsigned int*>(p);
   h->allocs.push_back(p);
   *out = h;
@@ -865,21 +907,22 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
   CRL_CUDA(h, cudaSetDevice(h->device));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int L = h->cfg.n_layers;
-  CRL_CUDA(h, cudaMemsetAsync(h->amax_dev, 0, sizeof(unsigned int) * 4 * L, s));
+  CRL_CUDA(h, cudaMemsetAsync(h->amax_dev, 0, sizeof(unsigned int) * 8 * L, s));
   crl_io io{};
   io.planes = planes; io.layout = layout; io.batch = batch; io.workspace = workspace; io.workspace_bytes = workspace_bytes;
   io.stream = stream;
   int rc = run_batch(h, &io, true);
   if (rc != CRL_OK) return rc;
-  std::vector<float> amax(4 * L);
-  CRL_CUDA(h, cudaMemcpyAsync(amax.data(), h->amax_dev, sizeof(float) * 4 * L, cudaMemcpyDeviceToHost, s));
+  std::vector<float> amax(8 * L);
+  CRL_CUDA(h, cudaMemcpyAsync(amax.data(), h->amax_dev, sizeof(float) * 8 * L, cudaMemcpyDeviceToHost, s));
   CRL_CUDA(h, cudaStreamSynchronize(s));
   auto mult = [](float a) { return a > 0.0f ? kFp8Max / a : 1.0f; };
   for (int l = 0; l < L; ++l) {
-    h->layers[l].sa_in = mult(amax[l * 4 + 0]);
-    h->layers[l].sa_ctx = mult(amax[l * 4 + 1]);
-    h->layers[l].sa_ffn = mult(amax[l * 4 + 2]);
-    h->layers[l].sa_hid = mult(amax[l * 4 + 3]);
+    h->layers[l].sa_in = mult(amax[l * 8 + 0]);
+    h->layers[l].sa_ctx = mult(amax[l * 8 + 1]);
+    h->layers[l].sa_ffn = mult(amax[l * 8 + 2]);
+    h->layers[l].sa_hid = mult(amax[l * 8 + 3]);
+    h->layers[l].sa_bias = mult(amax[l * 8 + 4]);
   }
   h->calibrated = true;
   return CRL_OK;
