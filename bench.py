@@ -108,6 +108,54 @@ def fp8_library_peak(device):
         return None
 
 
+def latency_b256(crl, synth, shapes_of, dims, smolgen, dtype, dev, runs=200, warm=20):
+    """p50 of one 256-position forward (the MCTS minibatch of the target's config 3), inputs resident,
+    timed per call with CUDA events; once with plain launches and once replayed from a CUDA graph."""
+    L, d, ff, H = dims
+    cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=smolgen, dtype=dtype)
+    eng = crl.Engine(cfg, dev.index)
+    eng.load_state_dict(synth.seeded_state_dict(shapes_of(cfg), seed=0))
+    planes = synth.synthetic_planes(256, 112, seed=7).to(dev)
+    bits = synth.synthetic_legal_bits(256, 1858, seed=8).to(dev)
+    if dtype == crl.DTYPE_F8E4M3:
+        eng.calibrate(planes)
+
+    def call():
+        return eng.forward(planes, legal_mask=bits, policy_softmax=True, policy_dtype=torch.float16)
+
+    def p50(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(runs):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2]
+
+    plain = p50(call)
+    graphed = None
+    try:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            call()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        graphed = p50(g.replay)
+    except Exception as e:           # graph capture is an optimisation, not a requirement
+        graphed = None
+    eng.close()
+    return {"p50_ms": plain, "p50_ms_cuda_graph": graphed, "runs": runs}
+
+
 def cpu_reference_forward(wl, sample, steps, warmup):
     """The oracle (fp32 PyTorch restatement of the reference forward) on all host threads."""
     from oracle import bt4spec
@@ -142,6 +190,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="global positions per step (default: the workload's)")
     ap.add_argument("--chunk", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-latency", action="store_true")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -259,6 +308,12 @@ def main():
                                       "launches": v["launches"]} for k, v in prof.items() if k != "gemm"},
                 "hbm_peak_gbs": peaks["hbm_gbs"]}
 
+    latency = None
+    if rank == 0 and world == 1 and not args.no_latency:
+        latency = {"batch": 256, "model": f"d{d} L{L} H{H} ff{ff}" + (" smolgen" if wl["smolgen"] else ""),
+                   "f16": latency_b256(crl, synth, _param_shapes, wl["dims"], wl["smolgen"], crl.DTYPE_F16, dev),
+                   "f8e4m3": latency_b256(crl, synth, _param_shapes, wl["dims"], wl["smolgen"], crl.DTYPE_F8E4M3, dev)}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample = 64 if d >= 1024 else 256
@@ -272,6 +327,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic", "config": config, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "latency_b256": latency,
             "device_status": st}))
     if dist is not None:
         dist.destroy_process_group()
