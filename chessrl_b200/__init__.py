@@ -4,6 +4,6 @@ from ._lib import (CrlError, LN_POST, LN_PRE, ACT_GELU, ACT_MISH, FFN_ACT_END, F
                    BIAS_RELPOS, BIAS_SMOLGEN, POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858, VALUE_NONE, VALUE_WDL,
                    VALUE_WDL_Q, DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8, MASK_NONE, MASK_BITS, MASK_ADDITIVE)
 from .engine import Engine, EngineConfig
-from .modules import BoardTransformer, BT4, BT4Planes19, BT4Baseline
+from .modules import BoardTransformer, BT4, BT4Planes19, BT4Baseline, GPT, GPTConfig
 
-__all__ = ["Engine", "EngineConfig", "BoardTransformer", "BT4", "BT4Planes19", "BT4Baseline", "CrlError"]
+__all__ = ["Engine", "EngineConfig", "BoardTransformer", "BT4", "BT4Planes19", "BT4Baseline", "GPT", "GPTConfig", "CrlError"]

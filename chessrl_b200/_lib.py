@@ -14,12 +14,13 @@ LN_POST, LN_PRE = 0, 1
 ACT_GELU, ACT_MISH = 1, 2
 FFN_ACT_END, FFN_ACT_MID = 0, 1
 BIAS_NONE, BIAS_CAUSAL, BIAS_RELPOS, BIAS_SMOLGEN = 0, 1, 2, 3
-POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858 = 0, 1, 2
+POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858, POLICY_LM_HEAD = 0, 1, 2, 3
 VALUE_NONE, VALUE_WDL, VALUE_WDL_Q = 0, 1, 2
 DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8 = 0, 1, 2
 LAYOUT_NHWC_F32, LAYOUT_NHWC_F16, LAYOUT_NCHW_F16, LAYOUT_NCHW_F32 = 0, 1, 2, 3
 MASK_NONE, MASK_BITS, MASK_ADDITIVE = 0, 1, 2
 OUT_F32, OUT_F16 = 0, 1
+VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
 
 EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
@@ -32,7 +33,8 @@ EXPORTS = [
 class Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "planes", "d_model", "n_layers", "n_heads", "d_ff", "ln_mode", "act", "ffn_act_pos", "bias_mode",
-        "policy_mode", "value_mode", "dtype", "smolgen_compress", "smolgen_hidden", "smolgen_gen", "chunk")]
+        "policy_mode", "value_mode", "dtype", "smolgen_compress", "smolgen_hidden", "smolgen_gen", "chunk", "pos_embed",
+        "lm_vocab")]
 
 
 class IO(ctypes.Structure):
@@ -45,6 +47,7 @@ class IO(ctypes.Structure):
         ("q_out", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
+        ("policy_vocab", ctypes.c_int32), ("black_rows", ctypes.c_void_p),
     ]
 
 

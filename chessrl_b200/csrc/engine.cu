@@ -72,10 +72,12 @@ struct crl_handle {
   float *lnF_w = nullptr, *lnF_b = nullptr, *b_pt = nullptr, *b_qk = nullptr;
   short* gather_idx = nullptr;
   signed char* gather_promo = nullptr;
+  short* mirror_idx = nullptr;
   std::vector<LayerW> layers;
   ValueW vh, vq;
 
   // crl_forward_host staging (device) and workspace, grown on demand
+  void* st_black = nullptr; size_t st_black_b = 0;
   void *st_planes = nullptr, *st_mask = nullptr, *st_policy = nullptr, *st_wdl = nullptr, *st_q = nullptr, *st_ws = nullptr;
   size_t st_planes_b = 0, st_mask_b = 0, st_policy_b = 0, st_wdl_b = 0, st_q_b = 0, st_ws_b = 0;
 };
@@ -119,10 +121,12 @@ void build_required(crl_handle* h) {
     r.push_back(t);
   if (c.bias_mode == CRL_BIAS_SMOLGEN) r.push_back("smolgen_shared.weight");
   if (c.ln_mode == CRL_LN_PRE) { r.push_back("norm_f.weight"); r.push_back("norm_f.bias"); }
-  if (c.policy_mode != CRL_POLICY_NONE)
+  if (c.policy_mode == CRL_POLICY_DENSE4096 || c.policy_mode == CRL_POLICY_GATHER1858)
     for (const char* t : {"policy_tokens_lin.weight", "policy_tokens_lin.bias", "queries_pol.weight", "queries_pol.bias",
                           "keys_pol.weight", "keys_pol.bias"})
       r.push_back(t);
+  if (c.policy_mode == CRL_POLICY_LM_HEAD) r.push_back("lm_head.weight");
+  if (c.pos_embed) r.push_back("pe");
   if (c.policy_mode == CRL_POLICY_DENSE4096) r.push_back("policy_head.weight");
   if (c.policy_mode == CRL_POLICY_GATHER1858) r.push_back("policy_promo.weight");
   if (c.value_mode != CRL_VALUE_NONE)
@@ -226,8 +230,9 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc) {
   w.sg_h2n = reinterpret_cast<__half*>(take(sg ? bc * hg * 2 : 0));
   w.sg_bias = reinterpret_cast<__half*>(take(sg ? static_cast<size_t>(bc) * c.n_heads * 4096 * 2 : 0));
   const bool dense = c.policy_mode == CRL_POLICY_DENSE4096;
+  const bool lm = c.policy_mode == CRL_POLICY_LM_HEAD;
   w.flat = reinterpret_cast<__half*>(take(dense ? static_cast<size_t>(bc) * 4096 * 2 : 0));
-  w.logits = reinterpret_cast<float*>(take(dense ? static_cast<size_t>(bc) * 1936 * 4 : 0));
+  w.logits = reinterpret_cast<float*>(take((dense || lm) ? static_cast<size_t>(bc) * 2048 * 4 : 0));
   w.v2 = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.total = off;
@@ -512,8 +517,29 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     if ((rc = value_head(h, h->vq, w.x, w.t1, w.v2q, bc, io->q_out + b0, 2, s)) != CRL_OK) return rc;
   }
 
+  // ---- last-token LM head of the decoder model (model_bis.py:369-370, 383-389) ----------------------------
+  if (c.policy_mode == CRL_POLICY_LM_HEAD && io->policy_out != nullptr) {
+    const int V = c.lm_vocab;
+    Lin e; e.a = w.x + static_cast<size_t>(63) * d; e.lda = static_cast<long long>(64) * d; e.w = h->w_ph; e.ldw = d;
+    e.c = w.logits; e.ldc = 2048; e.out = kOutF32; e.m = bc; e.n = V; e.k = d;
+    if ((rc = linear(h, e, s)) != CRL_OK) return rc;
+    const char* mask = static_cast<const char*>(io->legal_mask);
+    const void* mask_row = nullptr;
+    if (mask != nullptr && io->mask_mode == CRL_MASK_BITS) mask_row = mask + b0 * io->mask_stride;
+    if (mask != nullptr && io->mask_mode == CRL_MASK_ADDITIVE) mask_row = mask + b0 * io->mask_stride * 4;
+    MaskRowsParams m{};
+    m.logits = w.logits; m.ld = 2048; m.n = V; m.mask = mask_row; m.mask_mode = mask_row != nullptr ? io->mask_mode : CRL_MASK_NONE;
+    m.mask_ld = io->mask_stride; m.softmax = io->policy_softmax;
+    m.out_f32 = io->policy_dtype == CRL_OUT_F32 ? static_cast<float*>(io->policy_out) + b0 * io->policy_stride : nullptr;
+    m.out_f16 = io->policy_dtype == CRL_OUT_F16 ? static_cast<__half*>(io->policy_out) + b0 * io->policy_stride : nullptr;
+    m.out_ld = io->policy_stride;
+    mask_rows_kernel<<<static_cast<unsigned>(bc), 128, 0, s>>>(m);
+    CRL_CUDA(h, cudaGetLastError());
+    ++h->launches;
+  }
+
   // ---- policy head (value.py:173-187) -----------------------------------------------------------------
-  if (c.policy_mode != CRL_POLICY_NONE && io->policy_out != nullptr) {
+  if ((c.policy_mode == CRL_POLICY_DENSE4096 || c.policy_mode == CRL_POLICY_GATHER1858) && io->policy_out != nullptr) {
     Lin a; a.a = w.x; a.lda = d; a.w = h->w_pt; a.ldw = d; a.c = w.t2; a.ldc = d; a.m = M; a.n = d; a.k = d;
     a.bias = h->b_pt; a.act = kActGelu; a.res = h->pe16; a.ldr = d; a.res_mod = 64;
     if ((rc = linear(h, a, s)) != CRL_OK) return rc;
@@ -536,17 +562,21 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       p.gather_idx = h->gather_idx; p.gather_promo = h->gather_promo; p.n_moves = n_moves;
       p.mask = mask_row; p.mask_mode = mask_mode; p.mask_ld = io->mask_stride; p.softmax = io->policy_softmax;
       p.out_f32 = out32; p.out_f16 = out16; p.out_ld = io->policy_stride;
+      if (io->policy_vocab == CRL_VOCAB_RL1929) {
+        p.mirror = h->mirror_idx; p.out_width = 1929;
+        p.black_rows = io->black_rows != nullptr ? io->black_rows + b0 : nullptr;
+      }
     }
     ProfScope ps(h, s, kCatOther, 2.0 * bc * 64 * 64 * d, static_cast<double>(M) * 2 * d * 2 + static_cast<double>(bc) * n_moves * 4);
     policy_scores_kernel<<<static_cast<unsigned>(bc), 128, 0, s>>>(p);
     CRL_CUDA(h, cudaGetLastError());
     ++h->launches;
     if (c.policy_mode == CRL_POLICY_DENSE4096) {
-      Lin e; e.a = w.flat; e.lda = 4096; e.w = h->w_ph; e.ldw = 4096; e.c = w.logits; e.ldc = 1936; e.out = kOutF32;
+      Lin e; e.a = w.flat; e.lda = 4096; e.w = h->w_ph; e.ldw = 4096; e.c = w.logits; e.ldc = 2048; e.out = kOutF32;
       e.m = bc; e.n = 1929; e.k = 4096;
       if ((rc = linear(h, e, s)) != CRL_OK) return rc;
       MaskRowsParams m{};
-      m.logits = w.logits; m.ld = 1936; m.n = 1929; m.mask = mask_row; m.mask_mode = mask_mode; m.mask_ld = io->mask_stride;
+      m.logits = w.logits; m.ld = 2048; m.n = 1929; m.mask = mask_row; m.mask_mode = mask_mode; m.mask_ld = io->mask_stride;
       m.softmax = io->policy_softmax; m.out_f32 = out32; m.out_f16 = out16; m.out_ld = io->policy_stride;
       mask_rows_kernel<<<static_cast<unsigned>(bc), 128, 0, s>>>(m);
       CRL_CUDA(h, cudaGetLastError());
@@ -566,7 +596,11 @@ int check_io(crl_handle* h, const crl_io* io) {
   const int n_moves = crl_num_moves(h);
   if (io->policy_out != nullptr) {
     if (n_moves == 0) return fail(h, CRL_ERR_INVALID, "policy_out given but the configuration has no policy head");
-    if (io->policy_stride < n_moves) return fail(h, CRL_ERR_SHAPE, "policy_stride smaller than the move count");
+    if (io->policy_vocab != CRL_VOCAB_NATIVE && io->policy_vocab != CRL_VOCAB_RL1929) return fail(h, CRL_ERR_INVALID, "unknown policy_vocab");
+    if (io->policy_vocab == CRL_VOCAB_RL1929 && h->cfg.policy_mode != CRL_POLICY_GATHER1858)
+      return fail(h, CRL_ERR_INVALID, "policy_vocab RL1929 needs the 1858-move gather head");
+    if (io->policy_stride < (io->policy_vocab == CRL_VOCAB_RL1929 ? 1929 : n_moves))
+      return fail(h, CRL_ERR_SHAPE, "policy_stride smaller than the move count");
     if (io->policy_dtype != CRL_OUT_F32 && io->policy_dtype != CRL_OUT_F16) return fail(h, CRL_ERR_INVALID, "unknown policy dtype");
     if (io->legal_mask != nullptr && io->mask_mode == CRL_MASK_BITS && io->mask_stride * 8 < n_moves)
       return fail(h, CRL_ERR_SHAPE, "mask_stride too small for a bitset over the moves");
@@ -649,9 +683,10 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
   if (hd != 32 && hd != 64) return CRL_ERR_SHAPE;
   if (c.d_model % 64 != 0 || c.d_model > 1024 || c.d_ff % 16 != 0) return CRL_ERR_SHAPE;
   if (c.ln_mode < 0 || c.ln_mode > 1 || (c.act != CRL_ACT_GELU && c.act != CRL_ACT_MISH) || c.ffn_act_pos < 0 || c.ffn_act_pos > 1 ||
-      c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 2 || c.value_mode < 0 || c.value_mode > 2)
+      c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
   if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3) return CRL_ERR_UNSUPPORTED;
+  if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&
       (c.smolgen_compress <= 0 || c.smolgen_compress % 8 != 0 || c.smolgen_hidden % 8 != 0 || c.smolgen_hidden > 1024 ||
        c.smolgen_gen % 8 != 0 || c.smolgen_gen > 1024 || c.smolgen_hidden <= 0 || c.smolgen_gen <= 0))
@@ -688,7 +723,7 @@ void crl_destroy(crl_handle* h) {
   cudaSetDevice(h->device);
   for (void* p : h->allocs) cudaFree(p);
   for (auto& r : h->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
-  for (void* p : {h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
+  for (void* p : {h->st_black, h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
     if (p != nullptr) cudaFree(p);
   delete h;
 }
@@ -715,6 +750,7 @@ int crl_num_moves(const crl_handle* h) {
   if (h == nullptr) return 0;
   if (h->cfg.policy_mode == CRL_POLICY_DENSE4096) return 1929;
   if (h->cfg.policy_mode == CRL_POLICY_GATHER1858) return 1858;
+  if (h->cfg.policy_mode == CRL_POLICY_LM_HEAD) return h->cfg.lm_vocab;
   return 0;
 }
 
@@ -750,7 +786,8 @@ int crl_finalize(crl_handle* h) {
   ex.push_back({"ma_gating.a", 64 * d}); ex.push_back({"ma_gating.b", 64 * d});
   if (c.bias_mode == CRL_BIAS_SMOLGEN) ex.push_back({"smolgen_shared.weight", static_cast<size_t>(4096) * c.smolgen_gen});
   if (c.ln_mode == CRL_LN_PRE) { ex.push_back({"norm_f.weight", d}); ex.push_back({"norm_f.bias", d}); }
-  if (c.policy_mode != CRL_POLICY_NONE)
+  if (c.policy_mode == CRL_POLICY_LM_HEAD) ex.push_back({"lm_head.weight", static_cast<size_t>(c.lm_vocab) * d});
+  if (c.policy_mode == CRL_POLICY_DENSE4096 || c.policy_mode == CRL_POLICY_GATHER1858)
     for (const char* t : {"policy_tokens_lin", "queries_pol", "keys_pol"}) {
       ex.push_back({std::string(t) + ".weight", d * d}); ex.push_back({std::string(t) + ".bias", d});
     }
@@ -763,6 +800,11 @@ int crl_finalize(crl_handle* h) {
   };
   if (c.value_mode != CRL_VALUE_NONE) value_keys("value_head", 3);
   if (c.value_mode == CRL_VALUE_WDL_Q) value_keys("value_head_q", 1);
+  if (c.pos_embed) {
+    const std::vector<float>* v = get(h, "pe");
+    if (v == nullptr) return fail(h, CRL_ERR_MISSING_WEIGHT, "pe");
+    if (v->size() < 64 * d || v->size() % d != 0) return fail(h, CRL_ERR_SHAPE, "pe: expected [>=64, d_model]");
+  }
   for (const Expect& e : ex) {
     const std::vector<float>* v = get(h, e.key);
     if (v == nullptr) return fail(h, CRL_ERR_MISSING_WEIGHT, e.key);
@@ -796,7 +838,13 @@ int crl_finalize(crl_handle* h) {
     std::vector<float> ea(*get(h, "ma_gating.a"));
     for (float& x : ea) x = std::exp(x);
     if ((rc = upload_f32(h, &h->gate_ea, ea.data(), ea.size())) != CRL_OK) return rc;
-    UP32(h->gate_b, "ma_gating.b", 64 * d);
+    // positions added right after the gating (model_bis.py:363-366) fold into the gating offset
+    std::vector<float> gb(*get(h, "ma_gating.b"));
+    if (c.pos_embed) {
+      const std::vector<float>& pev = *get(h, "pe");
+      for (size_t i = 0; i < 64 * d; ++i) gb[i] += pev[i];
+    }
+    if ((rc = upload_f32(h, &h->gate_b, gb.data(), gb.size())) != CRL_OK) return rc;
   }
   for (int l = 0; l < c.n_layers; ++l) {
     LayerW& L = h->layers[l];
@@ -850,7 +898,8 @@ int crl_finalize(crl_handle* h) {
   }
   if (c.bias_mode == CRL_BIAS_SMOLGEN) UP16(h->sg_shared, "smolgen_shared.weight", 4096, c.smolgen_gen, c.smolgen_gen);
   if (c.ln_mode == CRL_LN_PRE) { UP32(h->lnF_w, "norm_f.weight", d); UP32(h->lnF_b, "norm_f.bias", d); }
-  if (c.policy_mode != CRL_POLICY_NONE) {
+  if (c.policy_mode == CRL_POLICY_LM_HEAD) UP16(h->w_ph, "lm_head.weight", c.lm_vocab, d, d);
+  if (c.policy_mode == CRL_POLICY_DENSE4096 || c.policy_mode == CRL_POLICY_GATHER1858) {
     UP16(h->w_pt, "policy_tokens_lin.weight", d, d, d); UP32(h->b_pt, "policy_tokens_lin.bias", d);
     const size_t rows = h->qk_ld;
     std::vector<float> wqk(rows * d, 0.0f), bqk(rows, 0.0f);
@@ -870,6 +919,9 @@ int crl_finalize(crl_handle* h) {
     if ((rc = dev_alloc(h, &h->gather_promo, v.promo.size())) != CRL_OK) return rc;
     CRL_CUDA(h, cudaMemcpy(h->gather_idx, v.from_to.data(), v.from_to.size() * sizeof(short), cudaMemcpyHostToDevice));
     CRL_CUDA(h, cudaMemcpy(h->gather_promo, v.promo.data(), v.promo.size(), cudaMemcpyHostToDevice));
+    std::vector<short> mir(v.mirror.begin(), v.mirror.end());
+    if ((rc = dev_alloc(h, &h->mirror_idx, mir.size())) != CRL_OK) return rc;
+    CRL_CUDA(h, cudaMemcpy(h->mirror_idx, mir.data(), mir.size() * sizeof(short), cudaMemcpyHostToDevice));
   }
   auto value_up = [&](ValueW& vw, const std::string& pre, int n_out) -> int {
     vw.n_out = n_out;
@@ -948,7 +1000,12 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
   if ((rc = grow(h, &h->st_ws, &h->st_ws_b, crl_workspace_bytes(h, io->batch))) != CRL_OK) return rc;
   CRL_CUDA(h, cudaMemcpyAsync(h->st_planes, io->planes, pb, cudaMemcpyHostToDevice, s));
   if (mb > 0) CRL_CUDA(h, cudaMemcpyAsync(h->st_mask, io->legal_mask, mb, cudaMemcpyHostToDevice, s));
+  if (io->black_rows != nullptr && io->policy_vocab == CRL_VOCAB_RL1929) {
+    if ((rc = grow(h, &h->st_black, &h->st_black_b, B)) != CRL_OK) return rc;
+    CRL_CUDA(h, cudaMemcpyAsync(h->st_black, io->black_rows, B, cudaMemcpyHostToDevice, s));
+  }
   crl_io dev = *io;
+  dev.black_rows = (io->black_rows != nullptr && io->policy_vocab == CRL_VOCAB_RL1929) ? static_cast<const uint8_t*>(h->st_black) : nullptr;
   dev.planes = h->st_planes;
   dev.legal_mask = mb > 0 ? h->st_mask : nullptr;
   dev.policy_out = ob > 0 ? h->st_policy : nullptr;

@@ -396,11 +396,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
           }
+          fence_proxy_async_smem();   // every writing lane, before the barrier (the documented order)
           __syncwarp();
           if (lane == 0) {
-            // one proxy fence by the issuing lane, after the warp barrier has ordered every lane's
-            // staging writes before it
-            fence_proxy_async_smem();
             tma_store_2d(&tmC, stage_u, c0, m0 + quarter * 32);
             bulk_commit();
           }

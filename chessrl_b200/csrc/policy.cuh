@@ -32,6 +32,11 @@ struct PolicyParams {
   const void* mask; int mask_mode; long long mask_ld;   // bits: bytes per row; additive: floats per row
   int softmax;
   float* out_f32; __half* out_f16; long long out_ld;
+  // optional scatter of the 1858 Leela entries into zero-filled rows of 1929 (Leela/compare_policy.py:
+  // 493-523): rows flagged in black_rows go through the rank-mirror table, the others keep their index
+  const short* mirror;          // [1858] or null
+  const uint8_t* black_rows;    // [B] (already offset to this chunk) or null = every row is White
+  int out_width;                // 1929 when scattering
 };
 
 __device__ __forceinline__ float block_reduce_128(float v, float* red, bool is_max) {
@@ -157,12 +162,22 @@ __global__ void __launch_bounds__(128) policy_scores_kernel(const PolicyParams p
 #pragma unroll
     for (int j = 0; j < PER; ++j) vals[j] *= inv;
   }
+  const bool scatter = p.mirror != nullptr;
+  const bool black = scatter && p.black_rows != nullptr && p.black_rows[board] != 0;
+  if (scatter) {
+    for (int o = threadIdx.x; o < p.out_width; o += 128) {
+      if (p.out_f32 != nullptr) p.out_f32[board * p.out_ld + o] = 0.0f;
+      else p.out_f16[board * p.out_ld + o] = __float2half_rn(0.0f);
+    }
+    __syncthreads();   // zero fill lands before the scattered values of other threads
+  }
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int m = threadIdx.x + j * 128;
     if (m < p.n_moves) {
-      if (p.out_f32 != nullptr) p.out_f32[board * p.out_ld + m] = vals[j];
-      else p.out_f16[board * p.out_ld + m] = __float2half_rn(vals[j]);
+      const int o = black ? p.mirror[m] : m;
+      if (p.out_f32 != nullptr) p.out_f32[board * p.out_ld + o] = vals[j];
+      else p.out_f16[board * p.out_ld + o] = __float2half_rn(vals[j]);
     }
   }
 }

@@ -28,6 +28,8 @@ class EngineConfig:
     smolgen_hidden: int = 256
     smolgen_gen: int = 256
     chunk: int = 0
+    pos_embed: int = 0
+    lm_vocab: int = 0
 
     @staticmethod
     def reference_value_q(n_layers=10, d_model=512, d_ff=736, n_heads=8, **kw):
@@ -46,6 +48,13 @@ class EngineConfig:
         return EngineConfig(112, d_model, n_layers, n_heads, d_ff, L.LN_POST, L.ACT_MISH, L.FFN_ACT_MID,
                             L.BIAS_SMOLGEN if smolgen else L.BIAS_NONE,
                             L.POLICY_NONE if value_only else L.POLICY_GATHER1858, L.VALUE_WDL, **kw)
+
+    @staticmethod
+    def reference_gpt(n_layer=6, n_head=12, n_embd=768, vocab_size=1929, **kw):
+        """Board-only path of `GPT(GPTConfig)` (model_bis.py:127-156, 358-370): 19 planes, pre-LN causal
+        blocks, GELU MLP 4x, final LayerNorm, last-token LM head."""
+        return EngineConfig(19, n_embd, n_layer, n_head, 4 * n_embd, L.LN_PRE, L.ACT_GELU, L.FFN_ACT_MID, L.BIAS_CAUSAL,
+                            L.POLICY_LM_HEAD, L.VALUE_NONE, pos_embed=1, lm_vocab=vocab_size, **kw)
 
     def to_c(self):
         return L.Config(**asdict(self))
@@ -136,10 +145,13 @@ class Engine:
 
     # ---- forward ---------------------------------------------------------------------------------
     def forward(self, planes, layout="nhwc", legal_mask=None, mask_mode=None, policy=True, wdl=True, q=False,
-                policy_softmax=False, wdl_softmax=True, policy_dtype=torch.float32, host=False):
+                policy_softmax=False, wdl_softmax=True, policy_dtype=torch.float32, host=False, rl_vocab=False,
+                black_rows=None):
         """planes: [..., 8, 8, P] ("nhwc") or [B, P, 8, 8] ("nchw"), on the engine's GPU (or on the host
         with host=True, which times like a user call: copies in, run, copies out, synchronise).
         legal_mask: uint8 bitset [B, ceil(V/8)] (bit m of row b: move m legal) or float32 additive [B, V].
+        rl_vocab=True (gather head): rows of 1929 in the reference's own vocabulary, Black rows (uint8 flags in
+        `black_rows`) rank-mirrored, like `map_leela_to_rl` after the server's softmax.
         Returns a dict with `policy` [B, V], `wdl` [B, 3], `q` [B] as requested and available."""
         planes = planes.contiguous()
         b = self._batch_of(planes, layout)
@@ -161,11 +173,17 @@ class Engine:
         want_policy = policy and self.n_moves > 0
         kw = dict(device=dev, pin_memory=True) if host else dict(device=dev)
         if want_policy:
-            out["policy"] = torch.empty(b, self.n_moves, dtype=policy_dtype, **kw)
+            width = 1929 if rl_vocab else self.n_moves
+            out["policy"] = torch.empty(b, width, dtype=policy_dtype, **kw)
             io.policy_out = out["policy"].data_ptr()
             io.policy_dtype = L.OUT_F32 if policy_dtype == torch.float32 else L.OUT_F16
             io.policy_softmax = int(policy_softmax)
-            io.policy_stride = self.n_moves
+            io.policy_stride = width
+            if rl_vocab:
+                io.policy_vocab = L.VOCAB_RL1929
+                if black_rows is not None:
+                    black_rows = black_rows.to(torch.uint8).contiguous()
+                    io.black_rows = black_rows.data_ptr()
         if wdl and self.cfg.value_mode != L.VALUE_NONE:
             out["wdl"] = torch.empty(b, 3, dtype=torch.float32, **kw)
             io.wdl_out = out["wdl"].data_ptr()

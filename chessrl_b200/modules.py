@@ -178,3 +178,135 @@ class BT4Baseline(BoardTransformer):
                  dtype=L.DTYPE_F16, engine_device=0, chunk=0):
         super().__init__(EngineConfig.baseline(num_layers, d_model, d_ff, num_heads, smolgen=smolgen,
                                                value_only=value_only, dtype=dtype, chunk=chunk), engine_device)
+
+
+# ------------------------------------------------------------------------------------------------------
+# Decoder model of model_bis.py, board-only inference path
+# ------------------------------------------------------------------------------------------------------
+from dataclasses import dataclass  # noqa: E402
+
+
+@dataclass
+class GPTConfig:
+    """Same fields as the reference's GPTConfig (model_bis.py:115-123)."""
+    block_size: int = 1024
+    vocab_size: int = 50304
+    n_layer: int = 6
+    n_head: int = 12
+    n_embd: int = 768
+    dropout: float = 0.0
+    bias: bool = True
+
+
+def _gpt_param_shapes(c: GPTConfig):
+    d = c.n_embd
+    shapes = {"FenEncoder.linear1.weight": (d, 19), "FenEncoder.linear1.bias": (d,),
+              "FenEncoder.layernorm1.weight": (d,), "FenEncoder.layernorm1.bias": (d,),
+              "FenEncoder.ma_gating.a": (64, d), "FenEncoder.ma_gating.b": (64, d),
+              "transformer.wte.weight": (c.vocab_size, d)}
+    for i in range(c.n_layer):
+        pre = f"transformer.h.{i}."
+        shapes[pre + "ln_1.weight"] = (d,)
+        shapes[pre + "attn.c_attn.weight"] = (3 * d, d)
+        shapes[pre + "attn.c_proj.weight"] = (d, d)
+        shapes[pre + "ln_2.weight"] = (d,)
+        shapes[pre + "mlp.c_fc.weight"] = (4 * d, d)
+        shapes[pre + "mlp.c_proj.weight"] = (d, 4 * d)
+        if c.bias:
+            for n, width in (("ln_1", d), ("attn.c_attn", 3 * d), ("attn.c_proj", d), ("ln_2", d), ("mlp.c_fc", 4 * d),
+                             ("mlp.c_proj", d)):
+                shapes[pre + n + ".bias"] = (width,)
+    shapes["transformer.ln_f.weight"] = (d,)
+    if c.bias:
+        shapes["transformer.ln_f.bias"] = (d,)
+    shapes["lm_head.weight"] = (c.vocab_size, d)
+    return shapes
+
+
+def gpt_to_engine_state_dict(sd, c: GPTConfig):
+    """Rename the reference GPT's tensors to the keys the engine uses (fused c_attn split into q/k/v, missing
+    biases of a bias=False model filled with zeros)."""
+    d = c.n_embd
+    out = {"linear1.weight": sd["FenEncoder.linear1.weight"], "linear1.bias": sd["FenEncoder.linear1.bias"],
+           "layernorm1.weight": sd["FenEncoder.layernorm1.weight"], "layernorm1.bias": sd["FenEncoder.layernorm1.bias"],
+           "ma_gating.a": sd["FenEncoder.ma_gating.a"], "ma_gating.b": sd["FenEncoder.ma_gating.b"],
+           "pe": sd["pe"], "lm_head.weight": sd["lm_head.weight"],
+           "norm_f.weight": sd["transformer.ln_f.weight"],
+           "norm_f.bias": sd.get("transformer.ln_f.bias", torch.zeros(d))}
+    for i in range(c.n_layer):
+        src, dst = f"transformer.h.{i}.", f"layers.{i}."
+        w = sd[src + "attn.c_attn.weight"]
+        b = sd.get(src + "attn.c_attn.bias", torch.zeros(3 * d))
+        for j, name in enumerate(("query_proj", "key_proj", "value_proj")):
+            out[dst + f"attention.{name}.weight"] = w[j * d:(j + 1) * d]
+            out[dst + f"attention.{name}.bias"] = b[j * d:(j + 1) * d]
+        out[dst + "attention.out_proj.weight"] = sd[src + "attn.c_proj.weight"]
+        out[dst + "attention.out_proj.bias"] = sd.get(src + "attn.c_proj.bias", torch.zeros(d))
+        out[dst + "norm1.weight"] = sd[src + "ln_1.weight"]
+        out[dst + "norm1.bias"] = sd.get(src + "ln_1.bias", torch.zeros(d))
+        out[dst + "norm2.weight"] = sd[src + "ln_2.weight"]
+        out[dst + "norm2.bias"] = sd.get(src + "ln_2.bias", torch.zeros(d))
+        out[dst + "ff1.weight"] = sd[src + "mlp.c_fc.weight"]
+        out[dst + "ff1.bias"] = sd.get(src + "mlp.c_fc.bias", torch.zeros(4 * d))
+        out[dst + "ff2.weight"] = sd[src + "mlp.c_proj.weight"]
+        out[dst + "ff2.bias"] = sd.get(src + "mlp.c_proj.bias", torch.zeros(d))
+    return out
+
+
+class GPT(nn.Module):
+    """`GPT(GPTConfig)` of model_bis.py:125-156 for board-only inference: the path of
+    `get_move_from_fen_no_thinking` (model_bis.py:358-398) up to the masked logits. The move-token part
+    of the sequence (`idx` beyond length 0) and training are not provided."""
+
+    def __init__(self, config: GPTConfig, dtype=L.DTYPE_F16, engine_device=0):
+        super().__init__()
+        self.config = config
+        d = config.n_embd
+        for name, shape in _gpt_param_shapes(config).items():
+            if name == "transformer.wte.weight":
+                continue
+            if name.endswith("ln_1.weight") or name.endswith("ln_2.weight") or name.endswith("ln_f.weight") \
+                    or name.endswith("layernorm1.weight") or name.endswith("ma_gating.b"):
+                init = torch.ones(shape)
+            elif name.endswith(".bias") or name.endswith("ma_gating.a"):
+                init = torch.zeros(shape)
+            else:
+                init = torch.randn(shape) * 0.02
+            _attach(self, name, nn.Parameter(init, requires_grad=False))
+        self.transformer.add_module("wte", _Node())
+        self.transformer.wte.register_parameter("weight", self.lm_head.weight)        # tied, both keys present
+        pos = torch.arange(config.block_size).unsqueeze(1)
+        import math
+        div = torch.exp(torch.arange(0, d, 2).float() * (-math.log(10000.0) / d))
+        pe = torch.zeros(config.block_size, d)
+        pe[:, 0::2] = torch.sin(pos * div)
+        pe[:, 1::2] = torch.cos(pos * div)
+        self.register_buffer("pe", pe)
+        self._cfg = EngineConfig.reference_gpt(config.n_layer, config.n_head, config.n_embd, config.vocab_size, dtype=dtype)
+        self._engine_device = engine_device
+        self._engine = None
+        self._pushed_versions = None
+
+    def engine(self):
+        if self._engine is None:
+            self._engine = Engine(self._cfg, self._engine_device)
+        versions = tuple((p.data_ptr(), p._version) for p in self.parameters())
+        if versions != self._pushed_versions:
+            self._engine.load_state_dict(gpt_to_engine_state_dict(self.state_dict(), self.config))
+            self._pushed_versions = versions
+        return self._engine
+
+    def board_logits(self, board, legal_mask=None, softmax=False):
+        """board [B,8,8,19] -> [B, vocab] logits of the last board token, optionally masked
+        (`logits + (1-mask)*(-999)`, model_bis.py:383) and soft-maxed."""
+        eng = self.engine()
+        return eng.forward(board.to(eng.device), legal_mask=legal_mask, policy_softmax=softmax, wdl=False)["policy"]
+
+    def forward(self, batch, compute_loss=False):
+        """batch = (board [B,8,8,19], idx [B,0]) -> (logits [B,1,V], None, targets [B,64]) as model_bis.py:171-199."""
+        board, idx = batch[0], batch[1]
+        if compute_loss or idx.numel() != 0:
+            raise NotImplementedError("inference engine: board-only path (empty move sequence) only")
+        logits = self.board_logits(board).unsqueeze(1)
+        targets = torch.roll(torch.full((board.shape[0], 64), 1928, dtype=torch.int64, device=logits.device), -1, 1)
+        return logits, None, targets

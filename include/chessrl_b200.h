@@ -36,16 +36,19 @@ enum { CRL_LN_POST = 0, CRL_LN_PRE = 1 };
 enum { CRL_ACT_GELU = 1, CRL_ACT_MISH = 2 };
 enum { CRL_FFN_ACT_END = 0, CRL_FFN_ACT_MID = 1 };
 enum { CRL_BIAS_NONE = 0, CRL_BIAS_CAUSAL = 1, CRL_BIAS_RELPOS = 2, CRL_BIAS_SMOLGEN = 3 };
-enum { CRL_POLICY_NONE = 0, CRL_POLICY_DENSE4096 = 1, CRL_POLICY_GATHER1858 = 2 };
+enum { CRL_POLICY_NONE = 0, CRL_POLICY_DENSE4096 = 1, CRL_POLICY_GATHER1858 = 2, CRL_POLICY_LM_HEAD = 3 };
 enum { CRL_VALUE_NONE = 0, CRL_VALUE_WDL = 1, CRL_VALUE_WDL_Q = 2 };
 enum { CRL_DTYPE_F16 = 0, CRL_DTYPE_F8E4M3 = 1, CRL_DTYPE_I8 = 2 };
 enum { CRL_LAYOUT_NHWC_F32 = 0, CRL_LAYOUT_NHWC_F16 = 1, CRL_LAYOUT_NCHW_F16 = 2, CRL_LAYOUT_NCHW_F32 = 3 };
 enum { CRL_MASK_NONE = 0, CRL_MASK_BITS = 1, CRL_MASK_ADDITIVE = 2 };
 enum { CRL_OUT_F32 = 0, CRL_OUT_F16 = 1 };
+enum { CRL_VOCAB_NATIVE = 0, CRL_VOCAB_RL1929 = 1 };
 
 /* Network description. Stands for the reference constructors
  *   BT4(num_layers, d_model, d_ff, num_heads)      new_paradigm/value.py:122, value_q.py:122
- * (planes 19 / 112 are fixed per class there: value.py:132, value_q.py:132); the remaining fields select
+ * (planes 19 / 112 are fixed per class there: value.py:132, value_q.py:132) and, with ln_mode PRE, bias_mode CAUSAL,
+ * pos_embed and CRL_POLICY_LM_HEAD, the board-only path of GPT(GPTConfig) (model_bis.py:127-156, 358-370), whose
+ * weights are passed under the BT4 key names (the Python module renames them); the remaining fields select
  * the variants of the target specification (Mish, activation position, pre-LN, smolgen, gather policy)
  * and the arithmetic type of the QKV / out-proj / FFN GEMMs. */
 typedef struct crl_config {
@@ -65,6 +68,8 @@ typedef struct crl_config {
   int32_t smolgen_hidden;   /* 256 */
   int32_t smolgen_gen;      /* 256 */
   int32_t chunk;            /* positions processed per pass over the layers; 0 = library default */
+  int32_t pos_embed;        /* 1: add the `pe` table [>=64, d] to the embedded tokens (model_bis.py:363-366) */
+  int32_t lm_vocab;         /* CRL_POLICY_LM_HEAD: rows of lm_head.weight (1929 in the reference's scripts) */
 } crl_config;
 
 /* One forward call. Stands for BT4.forward / get_batch_position_values (new_paradigm/value.py:155-212,
@@ -89,6 +94,11 @@ typedef struct crl_io {
   void* workspace;         /* device scratch, >= crl_workspace_bytes(h, batch) (ignored by _host) */
   size_t workspace_bytes;
   void* stream;            /* cudaStream_t, may be null (default stream) */
+  int32_t policy_vocab;    /* CRL_VOCAB_NATIVE: the head's own move list. CRL_VOCAB_RL1929 (gather head only): the
+                              1858 Leela entries scattered into zero-filled rows of 1929 like map_leela_to_rl
+                              (Leela/compare_policy.py:493-523); policy_stride >= 1929 */
+  const uint8_t* black_rows; /* nullable, [batch]: 1 = Black to move, the row goes through the rank-mirror table;
+                              0 / null = White, identity (the reference alternates rows: first_is_white) */
 } crl_io;
 
 /* Constructor: replaces BT4.__init__ (value.py:122-153). The device must be a B200 (sm_100). */
@@ -111,7 +121,7 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
                   size_t workspace_bytes, void* stream);
 
 size_t crl_workspace_bytes(const crl_handle* h, int64_t batch);
-int crl_num_moves(const crl_handle* h); /* 1929 (dense policy), 1858 (gather policy), 0 (none) */
+int crl_num_moves(const crl_handle* h); /* 1929 (dense policy), 1858 (gather policy), lm_vocab (LM head), 0 (none) */
 
 int crl_forward(crl_handle* h, const crl_io* io);
 /* Same call with HOST buffers: copies the planes (and mask) to the device, runs, copies results back and

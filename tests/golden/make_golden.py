@@ -112,6 +112,56 @@ def run_case(name, ref_cls, spec_cfg, dims, batch, seed, head_q):
     print(name, "ok", {k: getattr(v, "shape", None) for k, v in out.items()})
 
 
+def run_gpt_case(name, ref_root, seed):
+    """Board-only path of the reference GPT (body of get_move_from_fen_no_thinking, model_bis.py:358-370)."""
+    import io
+    import contextlib
+    from oracle import gptspec
+    cwd = os.getcwd()
+    os.chdir(ref_root)
+    with contextlib.redirect_stdout(io.StringIO()):
+        import model_bis
+        cfg = model_bis.GPTConfig(block_size=256, vocab_size=1929, n_layer=2, n_head=2, n_embd=128)
+        model = model_bis.GPT(cfg)
+    os.chdir(cwd)
+    spec = gptspec.GPTSpec(gptspec.GPTConfig(256, 1929, 2, 2, 128))
+    assert sorted(model.state_dict().keys()) == sorted(spec.state_dict().keys()), "GPT state_dict keys differ"
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for k in sorted(spec.state_dict().keys()):
+        v = spec.state_dict()[k]
+        if k == "pe":
+            sd[k] = v.clone()
+        elif k.endswith("ln_1.weight") or k.endswith("ln_2.weight") or k.endswith("ln_f.weight") or "layernorm1.weight" in k:
+            sd[k] = 1.0 + torch.randn(v.shape, generator=g) * 0.1
+        elif k.endswith("ma_gating.b"):
+            sd[k] = torch.ones(v.shape)
+        elif k.endswith("ma_gating.a"):
+            sd[k] = torch.randn(v.shape, generator=g) * 0.1
+        else:
+            sd[k] = torch.randn(v.shape, generator=g) * (0.1 if k.endswith(".bias") else 0.02)
+    sd["transformer.wte.weight"] = sd["lm_head.weight"]
+    model.load_state_dict(sd)
+    model.eval()
+    batch = 3
+    board = (torch.rand(batch, 8, 8, 19, generator=g) < 0.1).float()
+    board[..., 18] = (torch.rand(batch, 1, 1, generator=g) * 0.5).half().float().expand(batch, 8, 8)
+    with torch.no_grad():
+        x = model.FenEncoder(board) + model.pe[torch.arange(0, 64)]
+        for block in model.transformer.h:
+            x = block(x)
+        x = model.transformer.ln_f(x)
+        logits = model.lm_head(x[:, [-1], :])[:, 0]
+    spec.load_state_dict(sd)
+    spec.eval()
+    with torch.no_grad():
+        mine = spec.board_logits(board)
+    assert torch.equal(mine, logits), "GPT oracle differs from the reference"
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), board=board.numpy().astype(np.float16), logits=logits.numpy(),
+                        seed=np.array(seed), dims=np.array([2, 2, 128]))
+    print(name, "ok", tuple(logits.shape))
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     value_q, value = import_reference(ref_root)
@@ -122,6 +172,7 @@ def main():
              (2, 256, 320, 8), batch=2, seed=12, head_q=True)
     run_case("ref_value_L1_d64_ff64_h2", value.BT4, bt4spec.SpecConfig.reference_value(1, 64, 64, 2),
              (1, 64, 64, 2), batch=2, seed=13, head_q=False)
+    run_gpt_case("ref_gpt_L2_d128_h2", ref_root, seed=14)
 
 
 if __name__ == "__main__":

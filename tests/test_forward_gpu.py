@@ -52,7 +52,7 @@ def run_engine(spec_cfg, sd, tokens, **fw):
     return {k: v.float().cpu() for k, v in out.items()}, eng
 
 
-CASES = sorted(glob.glob(os.path.join(GOLDEN, "ref_*.npz")))
+CASES = sorted(glob.glob(os.path.join(GOLDEN, "ref_value*.npz")))
 
 
 @pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[:-4] for p in CASES])
@@ -219,3 +219,45 @@ def test_fp8_engine_tolerances():
     print(f"fp8: top-1 agreement over legal moves {agree:.4f} (over all 1858 logits {agree_unmasked:.4f}), "
           f"wdl err {werr:.3e}, policy max-abs err {perr:.3e}")
     assert agree >= 0.99 and werr <= 3e-2
+
+
+def test_rl_vocabulary_scatter_matches_map_leela_to_rl():
+    """1858 -> 1929 with rank mirroring for Black rows, fused into the policy kernel, against the oracle's
+    restatement of Leela/compare_policy.py:493-523 (index map exact, values untouched)."""
+    cfg = bt4spec.SpecConfig.baseline(1, 256, 512, 8, smolgen=False)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=16)
+    tokens = random_tokens(7, cfg.planes, seed=17)
+    native, eng = run_engine(cfg, sd, tokens, policy_softmax=True)
+    x = tokens.view(7, 8, 8, -1).cuda()
+    black = torch.tensor([0, 1, 0, 1, 0, 1, 0], dtype=torch.uint8)          # first_is_white=True
+    got = eng.forward(x, policy_softmax=True, rl_vocab=True, black_rows=black.cuda())["policy"].cpu()
+    want = torch.from_numpy(vocab.map_leela_to_rl(native["policy"].numpy(), first_is_white=True))
+    assert got.shape == (7, 1929) and torch.equal(got, want)
+    host = eng.forward(tokens.view(7, 8, 8, -1).half().pin_memory(), policy_softmax=True, rl_vocab=True,
+                       black_rows=black.pin_memory(), host=True)["policy"]
+    assert torch.equal(host, want)
+
+
+def test_gpt_board_only_path_against_reference_fixture():
+    """The decoder model's board-only forward (model_bis.py:358-370; pre-LN, causal, last-token LM head)
+    through the nn.Module drop-in, against logits of the unmodified reference GPT."""
+    from chessrl_b200 import GPT, GPTConfig
+    from oracle import gptspec
+    from test_oracle_golden import gpt_golden_state_dict
+    z = np.load(os.path.join(GOLDEN, "ref_gpt_L2_d128_h2.npz"))
+    n_layer, n_head, d = [int(v) for v in z["dims"]]
+    sd = gpt_golden_state_dict(gptspec.GPTSpec(gptspec.GPTConfig(256, 1929, n_layer, n_head, d)), int(z["seed"]))
+    model = GPT(GPTConfig(256, 1929, n_layer, n_head, d))
+    assert {k: tuple(v.shape) for k, v in model.state_dict().items()} == {k: tuple(v.shape) for k, v in sd.items()}
+    model.load_state_dict(sd)
+    board = torch.from_numpy(z["board"]).float()
+    logits, loss, targets = model((board, torch.zeros(board.shape[0], 0, dtype=torch.int64)))
+    assert logits.shape == (3, 1, 1929) and loss is None and targets.shape == (3, 64)
+    assert (logits[:, 0].cpu() - torch.from_numpy(z["logits"])).abs().max() <= POLICY_TOL
+    # masked, temperature-1 softmax as in model_bis.py:383-389
+    legal = torch.zeros(3, 1929, dtype=torch.bool)
+    legal[:, [3, 77, 1500, 1900]] = True
+    bits = torch.from_numpy(np.packbits(legal.numpy(), axis=1, bitorder="little")).cuda()
+    probs = model.board_logits(board, legal_mask=bits, softmax=True).cpu()
+    ref = torch.softmax(torch.from_numpy(z["logits"]) + (1 - legal.float()) * -999, -1)
+    assert (probs - ref).abs().max() <= 1e-2 and torch.equal(probs.argmax(-1), ref.argmax(-1))
