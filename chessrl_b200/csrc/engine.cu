@@ -33,6 +33,9 @@ struct LayerW {
   // FP8: e4m3 weights, the multipliers they were quantised with, and the activation multipliers
   uint8_t *wqkv8 = nullptr, *wo8 = nullptr, *wff1_8 = nullptr, *wff2_8 = nullptr;
   float sw_qkv = 1, sw_o = 1, sw_ff1 = 1, sw_ff2 = 1;
+  // INT8: per-output-channel symmetric weights and their scales
+  int8_t *wqkv_q = nullptr, *wo_q = nullptr, *wff1_q = nullptr, *wff2_q = nullptr;
+  float *cs_qkv = nullptr, *cs_o = nullptr, *cs_ff1 = nullptr, *cs_ff2 = nullptr;
   float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1;
 };
 
@@ -179,6 +182,26 @@ int upload_e4m3(crl_handle* h, uint8_t** out, float* mult, const float* src, siz
   return CRL_OK;
 }
 
+// per-output-channel symmetric int8: scale[n] = max|w[n,:]| / 127
+int upload_i8_rows(crl_handle* h, int8_t** out, float** scales, const float* src, size_t rows, size_t cols) {
+  std::vector<int8_t> q(rows * cols);
+  std::vector<float> sc(rows);
+  for (size_t r = 0; r < rows; ++r) {
+    float amax = 0.0f;
+    for (size_t c = 0; c < cols; ++c) amax = std::max(amax, std::fabs(src[r * cols + c]));
+    const float s1 = amax > 0.0f ? amax / 127.0f : 1.0f;
+    sc[r] = s1;
+    for (size_t c = 0; c < cols; ++c) {
+      const float v = std::nearbyint(src[r * cols + c] / s1);
+      q[r * cols + c] = static_cast<int8_t>(std::max(-127.0f, std::min(127.0f, v)));
+    }
+  }
+  int rc = dev_alloc(h, out, rows * cols);
+  if (rc != CRL_OK) return rc;
+  CRL_CUDA(h, cudaMemcpy(*out, q.data(), q.size(), cudaMemcpyHostToDevice));
+  return upload_f32(h, scales, sc.data(), rows);
+}
+
 struct Expect { std::string key; size_t numel; };
 
 const std::vector<float>* get(crl_handle* h, const std::string& k) {
@@ -190,6 +213,7 @@ const std::vector<float>* get(crl_handle* h, const std::string& k) {
 struct Workspace {
   __half *xin, *x, *xn, *t1, *t2, *y;
   uint8_t *x8, *t2_8, *t1_8;
+  float *xs, *t2s, *t1s;   // INT8: per-token scales of x8 / t2_8 / t1_8
   __half *sg_c, *sg_h1, *sg_h1n, *sg_h2, *sg_h2n, *sg_bias;
   __half *flat;     // [bc, 4096] policy scores (dense form)
   float* logits;    // [bc, 1929] f32 (dense form)
@@ -217,7 +241,11 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc) {
   w.t1 = reinterpret_cast<__half*>(take(M * wide * 2));
   w.t2 = reinterpret_cast<__half*>(take(M * d * 2));
   w.y = reinterpret_cast<__half*>(take(M * d * 2));
-  const bool f8 = c.dtype == CRL_DTYPE_F8E4M3;
+  const bool f8 = c.dtype == CRL_DTYPE_F8E4M3 || c.dtype == CRL_DTYPE_I8;
+  const bool rowsc = c.dtype == CRL_DTYPE_I8;
+  w.xs = reinterpret_cast<float*>(take(rowsc ? M * 4 : 0));
+  w.t2s = reinterpret_cast<float*>(take(rowsc ? M * 4 : 0));
+  w.t1s = reinterpret_cast<float*>(take(rowsc ? M * 4 : 0));
   w.x8 = reinterpret_cast<uint8_t*>(take(f8 ? M * d : 0));
   w.t2_8 = reinterpret_cast<uint8_t*>(take(f8 ? M * d : 0));
   w.t1_8 = reinterpret_cast<uint8_t*>(take(f8 ? M * c.d_ff : 0));
@@ -268,6 +296,7 @@ struct Lin {
   const float* bias = nullptr;
   const __half* res = nullptr; long long ldr = 0; int res_mod = 0;
   float alpha = 1.0f; int act = kActNone; float out_scale = 1.0f;
+  const float* row_scale = nullptr; const float* col_scale = nullptr;
 };
 
 int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
@@ -277,7 +306,7 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.M = static_cast<int>(l.m); g.p.N = l.n; g.p.K = l.k;
   g.p.C = l.c; g.p.ldc = l.ldc; g.p.out_dtype = l.out;
   g.p.bias = l.bias; g.p.residual = l.res; g.p.ldr = l.ldr; g.p.res_mod = l.res_mod;
-  g.p.alpha = l.alpha; g.p.row_scale = nullptr; g.p.col_scale = nullptr;
+  g.p.alpha = l.alpha; g.p.row_scale = l.row_scale; g.p.col_scale = l.col_scale;
   g.p.act = l.act; g.p.out_scale = l.out_scale; g.p.status = h->status_dev;
   const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
@@ -292,14 +321,24 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
 }
 
 int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const float* w, const float* b, __half* y,
-               uint8_t* y8, float y8_scale, const float* gate_ea, const float* gate_b, cudaStream_t s) {
+               uint8_t* y8, float y8_scale, const float* gate_ea, const float* gate_b, cudaStream_t s,
+               int8_t* yq = nullptr, float* yq_scale = nullptr) {
   LnParams p{};
   p.x = x; p.ldx = d; p.rows = rows; p.d = d; p.w = w; p.b = b;
   p.gate_ea = gate_ea; p.gate_b = gate_b;
   p.y = y; p.ldy = d; p.y8 = y8; p.ldy8 = d; p.out8_scale = y8_scale;
+  p.yq = yq; p.yq_scale = yq_scale;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * d * (2 + (y != nullptr ? 2 : 0) + (y8 != nullptr ? 1 : 0)));
   ln_rows_kernel<<<blocks, 256, 0, s>>>(p);
+  CRL_CUDA(h, cudaGetLastError());
+  ++h->launches;
+  return CRL_OK;
+}
+
+int quant_rows_i8(crl_handle* h, const __half* x, long long rows, int cols, uint8_t* q, float* scale, cudaStream_t s) {
+  ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * cols * 3);
+  quant_rows_i8_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(x, rows, cols, reinterpret_cast<int8_t*>(q), scale);
   CRL_CUDA(h, cudaGetLastError());
   ++h->launches;
   return CRL_OK;
@@ -366,6 +405,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   const int d = c.d_model, H = c.n_heads, ff = c.d_ff, P = c.planes;
   const long long M = bc * 64;
   const bool f8 = c.dtype == CRL_DTYPE_F8E4M3 && !calib;
+  const bool i8 = c.dtype == CRL_DTYPE_I8;
+  int8_t* const xq = reinterpret_cast<int8_t*>(w.x8);
   const int act = act_of(c);
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
@@ -399,7 +440,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     if ((rc = linear(h, e, s)) != CRL_OK) return rc;
     const bool emit8 = f8 && c.ln_mode == CRL_LN_POST;
     if ((rc = layer_norm(h, w.t2, M, d, h->lnE_w, h->lnE_b, w.x, emit8 ? w.x8 : nullptr,
-                         emit8 ? h->layers[0].sa_in : 1.0f, h->gate_ea, h->gate_b, s)) != CRL_OK)
+                         emit8 ? h->layers[0].sa_in : 1.0f, h->gate_ea, h->gate_b, s,
+                         (i8 && c.ln_mode == CRL_LN_POST) ? xq : nullptr, w.xs)) != CRL_OK)
       return rc;
   }
 
@@ -408,7 +450,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     const __half* attn_in = w.x;
     const uint8_t* attn_in8 = w.x8;
     if (c.ln_mode == CRL_LN_PRE) {
-      if ((rc = layer_norm(h, w.x, M, d, L.ln1w, L.ln1b, w.xn, f8 ? w.x8 : nullptr, L.sa_in, nullptr, nullptr, s)) != CRL_OK)
+      if ((rc = layer_norm(h, w.x, M, d, L.ln1w, L.ln1b, w.xn, f8 ? w.x8 : nullptr, L.sa_in, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK)
         return rc;
       attn_in = w.xn;
     }
@@ -417,6 +459,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     {
       Lin q; q.m = M; q.n = 3 * d; q.k = d; q.c = w.t1; q.ldc = 3 * d; q.bias = L.bqkv;
       if (f8) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); }
+      else if (i8) { q.kind = kKindI8; q.a = w.x8; q.w = L.wqkv_q; q.row_scale = w.xs; q.col_scale = L.cs_qkv; }
       else { q.a = attn_in; q.w = L.wqkv; }
       q.lda = d; q.ldw = d;
       if ((rc = linear(h, q, s)) != CRL_OK) return rc;
@@ -465,20 +508,22 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       ++h->launches;
     }
     if (calib && (rc = tap_amax(h, w.t2, M, d, l * 8 + 1, s)) != CRL_OK) return rc;
+    if (i8 && (rc = quant_rows_i8(h, w.t2, M, d, w.t2_8, w.t2s, s)) != CRL_OK) return rc;
     // out-proj + residual (+ LayerNorm for post-LN)
     {
       Lin o; o.m = M; o.n = d; o.k = d; o.bias = L.bo; o.res = w.x; o.ldr = d; o.lda = d; o.ldw = d;
       o.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; o.ldc = d;
       if (f8) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); }
+      else if (i8) { o.kind = kKindI8; o.a = w.t2_8; o.w = L.wo_q; o.row_scale = w.t2s; o.col_scale = L.cs_o; }
       else { o.a = w.t2; o.w = L.wo; }
       if ((rc = linear(h, o, s)) != CRL_OK) return rc;
     }
     const __half* ffn_in;
     if (c.ln_mode == CRL_LN_POST) {
-      if ((rc = layer_norm(h, w.y, M, d, L.ln1w, L.ln1b, w.x, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s)) != CRL_OK) return rc;
+      if ((rc = layer_norm(h, w.y, M, d, L.ln1w, L.ln1b, w.x, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
       ffn_in = w.x;
     } else {
-      if ((rc = layer_norm(h, w.x, M, d, L.ln2w, L.ln2b, w.xn, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s)) != CRL_OK) return rc;
+      if ((rc = layer_norm(h, w.x, M, d, L.ln2w, L.ln2b, w.xn, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
       ffn_in = w.xn;
     }
     if (calib && (rc = tap_amax(h, ffn_in, M, d, l * 8 + 2, s)) != CRL_OK) return rc;
@@ -487,20 +532,24 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       Lin a; a.m = M; a.n = ff; a.k = d; a.bias = L.bff1; a.lda = d; a.ldw = d; a.ldc = ff;
       a.act = c.ffn_act_pos == CRL_FFN_ACT_MID ? act : kActNone;
       if (f8) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; }
+      else if (i8) { a.kind = kKindI8; a.a = w.x8; a.w = L.wff1_q; a.row_scale = w.xs; a.col_scale = L.cs_ff1; a.c = w.t1; }
       else { a.a = ffn_in; a.w = L.wff1; a.c = w.t1; }
       if ((rc = linear(h, a, s)) != CRL_OK) return rc;
+      if (i8 && (rc = quant_rows_i8(h, w.t1, M, ff, w.t1_8, w.t1s, s)) != CRL_OK) return rc;
       if (calib && (rc = tap_amax(h, w.t1, M, ff, l * 8 + 3, s)) != CRL_OK) return rc;
       Lin b; b.m = M; b.n = d; b.k = ff; b.bias = L.bff2; b.lda = ff; b.ldw = ff; b.res = w.x; b.ldr = d;
       b.act = c.ffn_act_pos == CRL_FFN_ACT_END ? act : kActNone;
       b.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; b.ldc = d;
       if (f8) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); }
+      else if (i8) { b.kind = kKindI8; b.a = w.t1_8; b.w = L.wff2_q; b.row_scale = w.t1s; b.col_scale = L.cs_ff2; }
       else { b.a = w.t1; b.w = L.wff2; }
       if ((rc = linear(h, b, s)) != CRL_OK) return rc;
     }
     if (c.ln_mode == CRL_LN_POST) {
       const bool emit8 = f8 && l + 1 < c.n_layers;
       if ((rc = layer_norm(h, w.y, M, d, L.ln2w, L.ln2b, w.x, emit8 ? w.x8 : nullptr,
-                           emit8 ? h->layers[l + 1].sa_in : 1.0f, nullptr, nullptr, s)) != CRL_OK)
+                           emit8 ? h->layers[l + 1].sa_in : 1.0f, nullptr, nullptr, s,
+                           (i8 && l + 1 < c.n_layers) ? xq : nullptr, w.xs)) != CRL_OK)
         return rc;
     }
   }
@@ -685,7 +734,8 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
   if (c.ln_mode < 0 || c.ln_mode > 1 || (c.act != CRL_ACT_GELU && c.act != CRL_ACT_MISH) || c.ffn_act_pos < 0 || c.ffn_act_pos > 1 ||
       c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
-  if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3) return CRL_ERR_UNSUPPORTED;
+  if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3 && c.dtype != CRL_DTYPE_I8) return CRL_ERR_UNSUPPORTED;
+  if (c.dtype == CRL_DTYPE_I8 && (c.d_model % 16 != 0 || c.d_ff % 16 != 0)) return CRL_ERR_SHAPE;
   if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&
       (c.smolgen_compress <= 0 || c.smolgen_compress % 8 != 0 || c.smolgen_hidden % 8 != 0 || c.smolgen_hidden > 1024 ||
@@ -885,6 +935,12 @@ int crl_finalize(crl_handle* h) {
       UP32(L.sg_ln1w, lkey(l, "smolgen.ln1.weight"), hid); UP32(L.sg_ln1b, lkey(l, "smolgen.ln1.bias"), hid);
       UP16(L.sg_w2, lkey(l, "smolgen.dense2.weight"), H * gen, hid, hid); UP32(L.sg_b2, lkey(l, "smolgen.dense2.bias"), H * gen);
       UP32(L.sg_ln2w, lkey(l, "smolgen.ln2.weight"), gen); UP32(L.sg_ln2b, lkey(l, "smolgen.ln2.bias"), gen);
+    }
+    if (c.dtype == CRL_DTYPE_I8) {
+      if ((rc = upload_i8_rows(h, &L.wqkv_q, &L.cs_qkv, wqkv.data(), 3 * d, d)) != CRL_OK) return rc;
+      if ((rc = upload_i8_rows(h, &L.wo_q, &L.cs_o, get(h, lkey(l, "attention.out_proj.weight"))->data(), d, d)) != CRL_OK) return rc;
+      if ((rc = upload_i8_rows(h, &L.wff1_q, &L.cs_ff1, get(h, lkey(l, "ff1.weight"))->data(), ff, d)) != CRL_OK) return rc;
+      if ((rc = upload_i8_rows(h, &L.wff2_q, &L.cs_ff2, get(h, lkey(l, "ff2.weight"))->data(), d, ff)) != CRL_OK) return rc;
     }
     if (c.dtype == CRL_DTYPE_F8E4M3) {
       if ((rc = upload_e4m3(h, &L.wqkv8, &L.sw_qkv, wqkv.data(), wqkv.size())) != CRL_OK) return rc;

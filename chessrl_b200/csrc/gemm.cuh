@@ -56,13 +56,13 @@ struct GemmCfg {
   static constexpr uint32_t A_BYTES = BM * 128;
   static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int STAGES = PAIR ? 5 : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
-  // after the stages: the bias table [2][BN] f32, one 32-row x 64-byte staging tile per epilogue
+  // after the stages: the bias and column-scale tables [2][2][BN] f32, one 32-row x 64-byte staging tile per epilogue
   // warp (512-byte aligned: the TMA store swizzles by absolute address bits), then 128 bytes of
   // mbarriers + TMEM slot
   static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
-  static constexpr uint32_t BAR_OFF = EPI_OFF + 2 * BN * 4 + kEpiWarps * 2048;
+  static constexpr uint32_t BAR_OFF = EPI_OFF + 4 * BN * 4 + kEpiWarps * 2048;
   static constexpr uint32_t USED_BYTES = BAR_OFF + 128;
   static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + 896 /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
@@ -257,7 +257,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int part = ew >> 2;               // this warp takes the 32-column chunks part, part+4, ...
     const int et = threadIdx.x - 64;        // 0..511 among the epilogue threads
     float* bias_s = reinterpret_cast<float*>(smem + Cfg::EPI_OFF);                  // [2][BN]
-    const uint32_t stage_u = base + Cfg::EPI_OFF + 2 * BN * 4 + ew * 2048;          // 32 rows x 64 B
+    float* cs_s = bias_s + 2 * BN;                                                  // [2][BN] per-column scales
+    const uint32_t stage_u = base + Cfg::EPI_OFF + 4 * BN * 4 + ew * 2048;          // 32 rows x 64 B
     // 16-byte chunk q of staged row r; XOR swizzle keeps both access patterns bank-conflict free
     auto stage_off = [&](int r, int q) { return stage_u + r * 64 + ((q ^ ((r >> 1) & 3)) << 4); };
 
@@ -268,7 +269,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool al_cs = p.col_scale == nullptr || ((reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
     const bool vec_ok = al_c && al_r && al_b && al_cs;
     // staged path: f16 / e4m3 outputs on aligned buffers (the shapes of the network's hot GEMMs)
-    const bool staged_ok = p.use_tma_store != 0 && al_r && p.col_scale == nullptr && p.out_dtype != kOutF32;
+    const bool staged_ok = p.use_tma_store != 0 && al_r && p.out_dtype != kOutF32;
     bool alive = true;
     int local = 0;
     for (int t = worker; t < num_tiles; t += num_workers, ++local) {
@@ -279,6 +280,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // this tile's bias slice goes to shared memory while the MMAs are still running
       if (p.bias != nullptr) {
         for (int e = et; e < BN; e += kEpiWarps * 32) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
+      }
+      if (p.col_scale != nullptr) {
+        for (int e = et; e < BN; e += kEpiWarps * 32) cs_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.col_scale + n0 + e) : 0.0f;
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
       if (alive && !mbar_wait(tfull_bar(as), aph)) {
@@ -322,6 +326,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           else v[j] = __uint_as_float(acc[j]) * a_scale;
         }
         if (staged) {
+          if (p.col_scale != nullptr) {
+            const float4* c4p = reinterpret_cast<const float4*>(cs_s + as * BN + c * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 c4 = c4p[q];
+              v[q * 4] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+            }
+          }
           if (p.bias != nullptr) {
             const float4* b4p = reinterpret_cast<const float4*>(bias_s + as * BN + c * 32);
 #pragma unroll

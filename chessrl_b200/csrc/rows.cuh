@@ -63,6 +63,7 @@ struct LnParams {
   const float* gate_ea; const float* gate_b;   // [64, d] or null
   __half* y; long long ldy;                    // nullable
   uint8_t* y8; long long ldy8; float out8_scale;  // nullable
+  int8_t* yq; float* yq_scale;                 // nullable: per-row symmetric int8 (row scale = max|y| / 127)
 };
 
 __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
@@ -106,6 +107,28 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
   for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
   const float rstd = rsqrtf(var / p.d + 1e-5f);
   const int tok = static_cast<int>(row & 63);
+  float qinv = 0.0f;
+  if (p.yq != nullptr) {
+    // dynamic per-token int8: one extra pass over the registers for the row maximum of |y|
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < p.d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float yy = (v[i][j] - mean) * rstd * __ldg(p.w + c + j) + __ldg(p.b + c + j);
+          if (p.gate_ea != nullptr) yy = yy * __ldg(p.gate_ea + (long long)tok * p.d + c + j) + __ldg(p.gate_b + (long long)tok * p.d + c + j);
+          amax = fmaxf(amax, fabsf(yy));
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+    qinv = 1.0f / sc;
+    if (lane == 0) p.yq_scale[row] = sc;
+  }
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int c = (i * 32 + lane) * 8;
@@ -146,6 +169,12 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
         uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(y[4] * s, y[5] * s), __NV_SATFINITE, __NV_E4M3) |
                       (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(y[6] * s, y[7] * s), __NV_SATFINITE, __NV_E4M3)) << 16);
         *reinterpret_cast<uint2*>(p.y8 + row * p.ldy8 + c) = make_uint2(lo, hi);
+      }
+      if (p.yq != nullptr) {
+        __align__(8) signed char q8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q8[j] = static_cast<signed char>(max(-127, min(127, __float2int_rn(y[j] * qinv))));
+        *reinterpret_cast<uint2*>(p.yq + row * p.d + c) = *reinterpret_cast<const uint2*>(q8);
       }
     }
   }
@@ -202,6 +231,43 @@ __global__ void absmax_f16_kernel(const __half* __restrict__ x, long long rows, 
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
+}
+
+// f16 rows -> per-row symmetric int8 + scale (dynamic per-token activation quantisation); one warp per row,
+// cols a multiple of 8.
+__global__ void __launch_bounds__(256) quant_rows_i8_kernel(const __half* __restrict__ x, long long rows, int cols,
+                                                            int8_t* __restrict__ q, float* __restrict__ scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const __half* xr = x + row * cols;
+  float amax = 0.0f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+  const float inv = 1.0f / sc;
+  if (lane == 0) scale[row] = sc;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);   // second read hits L1/L2
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    __align__(8) signed char q8[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      q8[2 * j] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.x * inv))));
+      q8[2 * j + 1] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.y * inv))));
+    }
+    *reinterpret_cast<uint2*>(q + row * cols + c) = *reinterpret_cast<const uint2*>(q8);
+  }
 }
 
 // f16 -> e4m3 with a per-tensor scale (used where the producer kernel cannot emit e4m3 itself)

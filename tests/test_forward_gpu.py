@@ -261,3 +261,35 @@ def test_gpt_board_only_path_against_reference_fixture():
     probs = model.board_logits(board, legal_mask=bits, softmax=True).cpu()
     ref = torch.softmax(torch.from_numpy(z["logits"]) + (1 - legal.float()) * -999, -1)
     assert (probs - ref).abs().max() <= 1e-2 and torch.equal(probs.argmax(-1), ref.argmax(-1))
+
+
+@pytest.mark.parametrize("value_only", [True, False])
+def test_int8_w8a8_engine_tolerances(value_only):
+    """INT8 W8A8 on the QKV / out-proj / FFN GEMMs (per-output-channel symmetric weights, per-token dynamic
+    activations, int32 accumulation) against the FP32 oracle: WDL within 3e-2; with a policy head, top-1
+    agreement over the legal moves >= 99 %. value_only is the WDL-only network of the target's config 5."""
+    from chessrl_b200 import Engine, synth
+    cfg = bt4spec.SpecConfig.baseline(8, 256, 1024, 8, smolgen=True, value_only=value_only)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=31)
+    b = 1024 if not value_only else 256
+    tokens = random_tokens(b, cfg.planes, seed=32)
+    ref = oracle_out(cfg, sd, tokens)
+    eng = Engine(engine_cfg(cfg, dtype=2))
+    eng.load_state_dict(sd)
+    x = tokens.view(b, 8, 8, -1).cuda()
+    bits = synth.synthetic_legal_bits(b, 1858, seed=33)
+    out = eng.forward(x, legal_mask=None if value_only else bits.cuda())
+    rc, st = eng.last_status()
+    assert rc == 0 and st == 0
+    werr = (out["wdl"].cpu() - torch.softmax(ref["wdl"], -1)).abs().max().item()
+    msg = f"int8: wdl err {werr:.3e}"
+    if not value_only:
+        legal = torch.from_numpy(np.unpackbits(bits.numpy(), axis=1, bitorder="little")[:, :1858].astype(bool))
+        ref_masked = bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal)
+        agree = (out["policy"].cpu().argmax(-1) == ref_masked.argmax(-1)).float().mean().item()
+        msg += f", top-1 agreement over legal moves {agree:.4f}"
+        assert agree >= 0.99
+    else:
+        assert "policy" not in out
+    print(msg)
+    assert werr <= 3e-2
