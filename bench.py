@@ -30,7 +30,10 @@ WORKLOADS = {
     "c3": dict(dims=(15, 1024, 1536, 32), smolgen=True, dtype="f16", batch=1024),
     "c3_b256": dict(dims=(15, 1024, 1536, 32), smolgen=True, dtype="f16", batch=256),
     "c2": dict(dims=(8, 256, 1024, 8), smolgen=False, dtype="f16", batch=4096),
+    # config 5: INT8 W8A8, WDL head only; --sweep adds the batch sweep against FP16
+    "c5": dict(dims=(15, 1024, 1536, 32), smolgen=True, dtype="i8", batch=16384, value_only=True),
 }
+DTYPES = {"f16": 0, "f8e4m3": 1, "i8": 2}
 
 
 def flops_per_position(L, d, ff, H, smolgen, P=112, policy=True):
@@ -191,6 +194,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="config 5 batch sweep (1..16384) of INT8 against FP16")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -199,7 +203,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    fpp = flops_per_position(L, d, ff, H, wl["smolgen"])
+    value_only = bool(wl.get("value_only"))
+    fpp = flops_per_position(L, d, ff, H, wl["smolgen"], policy=not value_only)
     config = {"workload": f"{args.workload}: BT4-shaped encoder d{d} L{L} H{H} ff{ff}" + (" smolgen" if wl["smolgen"] else "") +
                           f" gather-policy-1858+mask+softmax WDL, {wl['dtype']}, {wl['batch']} positions/step",
               "global_batch": wl["batch"], "parallelism": f"replicas x{world} (positions sharded, weights replicated)",
@@ -231,8 +236,8 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     per_rank = wl["batch"] // world
-    dtype = crl.DTYPE_F8E4M3 if wl["dtype"] == "f8e4m3" else crl.DTYPE_F16
-    cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], dtype=dtype, chunk=args.chunk)
+    dtype = DTYPES[wl["dtype"]]
+    cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only, dtype=dtype, chunk=args.chunk)
     eng = crl.Engine(cfg, local_rank)
     eng.load_state_dict(synth.seeded_state_dict(_param_shapes(cfg), seed=0))
     planes_host = synth.synthetic_planes(per_rank, 112, seed=1000 + rank).pin_memory()
@@ -242,10 +247,11 @@ def main():
         eng.calibrate(planes[: min(per_rank, 2048)])
 
     def step():
-        return eng.forward(planes, legal_mask=bits, policy_softmax=True, policy_dtype=torch.float16)
+        return eng.forward(planes, legal_mask=None if value_only else bits, policy_softmax=True, policy_dtype=torch.float16)
 
     def step_host():
-        return eng.forward(planes_host, legal_mask=bits_host, policy_softmax=True, policy_dtype=torch.float16, host=True)
+        return eng.forward(planes_host, legal_mask=None if value_only else bits_host, policy_softmax=True,
+                           policy_dtype=torch.float16, host=True)
 
     def barrier():
         torch.cuda.synchronize()
@@ -282,7 +288,7 @@ def main():
     ms_e2e = timed(step_host, args.steps) / args.steps
     e2e = {"value": wl["batch"] / (ms_e2e * 1e-3), "unit": "positions/s",
            "h2d_bytes_per_step": (planes_host.numel() * 2 + bits_host.numel()) * world,
-           "d2h_bytes_per_step": (per_rank * 1858 * 2 + per_rank * 12) * world}
+           "d2h_bytes_per_step": ((0 if value_only else per_rank * 1858 * 2) + per_rank * 12) * world}
 
     # per-kernel pass (untimed): CUDA events around every launch, on the launch stream
     eng.profile(True)
@@ -290,7 +296,7 @@ def main():
     prof = eng.profile_read()
     eng.profile(False)
     peaks, peak_kind = measured_peaks()
-    if dtype == crl.DTYPE_F8E4M3:
+    if dtype != crl.DTYPE_F16:
         lib_peak = fp8_library_peak(dev)
         peak = lib_peak if lib_peak else 2.0 * peaks["bf16_tflops"]
         peak_note = ("live torch._scaled_mm e4m3 8192^3 burst on this GPU (MEASURED_PEAKS.json has no FP8 figure)"
@@ -307,6 +313,29 @@ def main():
                 "other_kernels": {k: {"ms": v["ms"], "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] else None,
                                       "launches": v["launches"]} for k, v in prof.items() if k != "gemm"},
                 "hbm_peak_gbs": peaks["hbm_gbs"]}
+
+    sweep = None
+    if args.sweep and rank == 0 and world == 1:
+        # batch sweep of config 5: INT8 against FP16 on the same network, positions/s per batch size
+        sweep = {}
+        for name, dt in (("i8", crl.DTYPE_I8), ("f16", crl.DTYPE_F16)):
+            e2 = crl.Engine(crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only, dtype=dt), local_rank)
+            e2.load_state_dict(synth.seeded_state_dict(_param_shapes(e2.cfg), seed=0))
+            sweep[name] = {}
+            for bsz in (1, 16, 256, 4096, 16384):
+                pl = planes[:bsz]
+                for _ in range(3):
+                    e2.forward(pl, policy=not value_only)
+                torch.cuda.synchronize()
+                reps = 20 if bsz <= 256 else 3
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    e2.forward(pl, policy=not value_only)
+                e1.record()
+                torch.cuda.synchronize()
+                sweep[name][str(bsz)] = bsz / (e0.elapsed_time(e1) / reps * 1e-3)
+            e2.close()
 
     latency = None
     if rank == 0 and world == 1 and not args.no_latency:
@@ -327,7 +356,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic", "config": config, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "latency_b256": latency,
+            "latency_b256": latency, "batch_sweep_positions_per_s": sweep,
             "device_status": st}))
     if dist is not None:
         dist.destroy_process_group()
