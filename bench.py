@@ -118,8 +118,9 @@ def latency_b256(crl, synth, shapes_of, dims, smolgen, dtype, dev, runs=200, war
     cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=smolgen, dtype=dtype)
     eng = crl.Engine(cfg, dev.index)
     eng.load_state_dict(synth.seeded_state_dict(shapes_of(cfg), seed=0))
-    planes = synth.synthetic_planes(256, 112, seed=7).to(dev)
-    bits = synth.synthetic_legal_bits(256, 1858, seed=8).to(dev)
+    from chessrl_b200 import positions
+    pos = positions.playout_positions(256, seed=7, max_plies=80)
+    planes, bits = pos["planes112"].to(dev), pos["legal1858"].to(dev)
     if dtype == crl.DTYPE_F8E4M3:
         eng.calibrate(planes)
 
@@ -240,8 +241,11 @@ def main():
     cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only, dtype=dtype, chunk=args.chunk)
     eng = crl.Engine(cfg, local_rank)
     eng.load_state_dict(synth.seeded_state_dict(_param_shapes(cfg), seed=0))
-    planes_host = synth.synthetic_planes(per_rank, 112, seed=1000 + rank).pin_memory()
-    bits_host = synth.synthetic_legal_bits(per_rank, 1858, seed=2000 + rank).pin_memory()
+    # seeded random playouts of 0..80 plies from the start position (the workload's stated input distribution):
+    # 112-plane history encoding + legal-move bitsets from the library's own move generator
+    from chessrl_b200 import positions
+    pos = positions.playout_positions(per_rank, seed=20240607, first=rank * per_rank, max_plies=80, pin_memory=True)
+    planes_host, bits_host = pos["planes112"], pos["legal1858"]
     planes, bits = planes_host.to(dev), bits_host.to(dev)
     if dtype == crl.DTYPE_F8E4M3:
         eng.calibrate(planes[: min(per_rank, 2048)])
@@ -354,7 +358,8 @@ def main():
         print(json.dumps({
             "metric": "positions/sec", "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic", "config": config, "e2e": e2e,
+            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded random-playout positions, random-init weights)",
+            "config": config, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "latency_b256": latency, "batch_sweep_positions_per_s": sweep,
             "device_status": st}))

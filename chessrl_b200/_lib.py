@@ -26,7 +26,8 @@ EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
-    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static",
+    "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static", "crl_perft", "crl_fen_to_planes19", "crl_legal_mask_1929",
+    "crl_playout_positions",
 ]
 
 
@@ -109,6 +110,14 @@ def load():
     lib.crl_linear.argtypes = [ctypes.c_int, vp, i64, vp, i64, vp, i64, ctypes.c_int, i64, i64, i64, vp, vp, i64,
                                ctypes.c_float, ctypes.c_int, vp, vp]
     lib.crl_linear.restype = ctypes.c_int
+    lib.crl_perft.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_uint64)]
+    lib.crl_perft.restype = ctypes.c_int
+    lib.crl_fen_to_planes19.argtypes = [ctypes.c_char_p, vp]
+    lib.crl_fen_to_planes19.restype = ctypes.c_int
+    lib.crl_legal_mask_1929.argtypes = [ctypes.c_char_p, vp]
+    lib.crl_legal_mask_1929.restype = ctypes.c_int
+    lib.crl_playout_positions.argtypes = [ctypes.c_uint64, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp]
+    lib.crl_playout_positions.restype = ctypes.c_int
     lib.crl_vocab_move.argtypes = [ctypes.c_int, ctypes.c_char_p]
     lib.crl_vocab_move.restype = ctypes.c_int
     lib.crl_vocab_mirror_index.argtypes = [ctypes.c_int]

@@ -174,6 +174,31 @@ int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw,
                int out_dtype, int64_t m, int64_t n, int64_t k, const float* bias, const void* residual,
                int64_t ldr, float alpha, int act, int* device_status, void* stream);
 
+/* ---- host-side input producers (no GPU needed) ------------------------------------------------------------
+ * The reference builds its inputs with python-chess; these entry points are the library's own rules
+ * implementation (validated by perft counts and against the test oracle). */
+
+/* Number of leaf nodes of the legal-move tree of depth 1..8 below `fen` (null = start position). */
+int crl_perft(const char* fen, int depth, uint64_t* nodes);
+/* fen_to_tensor (utils/fen_encoder.py:5-38): FEN -> [8,8,19] f32, row 0 = rank 8. */
+int crl_fen_to_planes19(const char* fen, float* out);
+/* Legal-move bitset over the 1929 vocabulary (242 bytes, bit m = entry m legal; a knight promotion sets the
+ * 4-character move), the index set of model_bis.py:373-380. */
+int crl_legal_mask_1929(const char* fen, uint8_t* bits);
+/* Seeded random playouts from the start position (plies ~ U{0..max_plies}, uniformly random legal moves, a
+ * finished game restarts): positions first .. first+count-1 of the stream `seed`. Every output is optional:
+ *   planes112_f16 [count,64,112]  the server input in token-major f16 (history of 8 boards in the mover's view,
+ *                                 Leela/gen_TC.py:255-319 + pgn_to_input_data_decoder.py:61-72 + ustotheirs.py:4-23;
+ *                                 plane 109 = halfmove/100 when rule50_plane is set, else empty)
+ *   planes19_f32  [count,8,8,19]  utils/fen_encoder.py:5-38
+ *   legal1858     [count,233]     bitset over the Leela entries from the mover's view (pgn_to_input_data_decoder.py:35-42)
+ *   legal1929     [count,242]     bitset over the 1929 vocabulary (model_bis.py:373-380)
+ *   black         [count]         1 = Black to move
+ *   fens          [count,96]      zero-terminated FEN strings */
+int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t max_plies, int32_t rule50_plane,
+                          uint16_t* planes112_f16, float* planes19_f32, uint8_t* legal1858, uint8_t* legal1929,
+                          uint8_t* black, char* fens);
+
 /* Move vocabulary (utils/vocab.py:9-438): writes the UCI string of entry `index` of the 1929-entry
  * list into buf (>= 16 bytes); entries < 1858 are the Leela list. Returns 0, or CRL_ERR_INVALID. */
 int crl_vocab_move(int index, char* buf);

@@ -1,0 +1,81 @@
+"""Chess rules and input encoders (no GPU): the library's C++ implementation and the oracle's independent
+Python restatement against the well-known perft node counts, and against each other position by position
+(moves, FENs, 19 planes, 112 planes, legal-move bitsets: all exact)."""
+import numpy as np
+import pytest
+
+from oracle import chesspos, vocab
+
+KIWIPETE = "r3k2r/p1ppqpb1/bn2pnp1/3PN3/1p2P3/2N2Q1p/PPPBBPPP/R3K2R w KQkq - 0 1"
+ENDGAME = "8/2p5/3p4/KP5r/1R3p1k/8/4P1P1/8 w - - 0 1"
+PROMO = "r3k2r/Pppp1ppp/1b3nbN/nP6/BBP1P3/q4N2/Pp1P2PP/R2Q1RK1 w kq - 0 1"
+
+
+@pytest.mark.parametrize("fen,counts", [
+    (None, [20, 400, 8902, 197281]),
+    (KIWIPETE, [48, 2039, 97862]),
+    (ENDGAME, [14, 191, 2812, 43238]),
+    (PROMO, [6, 264, 9467]),
+])
+def test_library_perft(lib, fen, counts):
+    from chessrl_b200 import positions
+    for depth, want in enumerate(counts, start=1):
+        assert positions.perft(fen, depth) == want
+
+
+def test_library_perft_depth5_start(lib):
+    from chessrl_b200 import positions
+    assert positions.perft(None, 5) == 4865609
+
+
+@pytest.mark.parametrize("fen,counts", [
+    (chesspos.START_FEN, [20, 400, 8902]),
+    (KIWIPETE, [48, 2039]),
+    (ENDGAME, [14, 191, 2812]),
+    (PROMO, [6, 264]),
+])
+def test_oracle_perft(fen, counts):
+    for depth, want in enumerate(counts, start=1):
+        assert chesspos.perft(chesspos.Position(fen), depth) == want
+
+
+def test_playouts_planes_and_masks_match_oracle(lib):
+    from chessrl_b200 import positions
+    n, seed = 160, 20240607
+    got = positions.playout_positions(n, seed=seed, max_plies=80, planes19=True, fens=True)
+    p112 = got["planes112"].float().numpy().reshape(n, 64, 112)
+    for i in range(n):
+        hist = chesspos.playout(seed, i, 80)
+        cur = hist[0]
+        assert got["fens"][i] == cur.fen()
+        assert int(got["black"][i]) == cur.turn
+        np.testing.assert_array_equal(got["planes19"][i].numpy(), chesspos.planes19(cur))
+        want112 = chesspos.planes112(hist, rule50=True)
+        np.testing.assert_array_equal(p112[i], want112.astype(np.float16).astype(np.float32))
+        np.testing.assert_array_equal(got["legal1929"][i].numpy(), chesspos.legal_bits(cur, 1929))
+        view = cur.mirror() if cur.turn == chesspos.BLACK else cur
+        np.testing.assert_array_equal(got["legal1858"][i].numpy(), chesspos.legal_bits(view, 1858))
+    plies = [len(chesspos.playout(seed, i, 80)) for i in range(40)]
+    assert min(plies) < 8 <= max(plies)           # short games (empty history steps) and full histories both occur
+
+
+def test_fen_entry_points(lib):
+    from chessrl_b200 import positions
+    for fen in (chesspos.START_FEN, KIWIPETE, PROMO, "rnbqkbnr/pppp1ppp/8/4p3/4P3/8/PPPP1PPP/RNBQKBNR w KQkq e6 3 2"):
+        pos = chesspos.Position(fen)
+        np.testing.assert_array_equal(positions.fen_to_tensor(fen), chesspos.planes19(pos))
+        np.testing.assert_array_equal(positions.legal_mask_1929(fen), chesspos.legal_bits(pos, 1929))
+    # knight promotion folds onto the 4-character token (model_bis.py:376-379)
+    bits = np.unpackbits(positions.legal_mask_1929(PROMO), bitorder="little")
+    assert bits[vocab.policy_index.index("b7b8")] == 1 or bits[vocab.policy_index.index("a7a8")] == 0
+    with pytest.raises(Exception):
+        positions.fen_to_tensor("not a fen")
+
+
+def test_mirror_symmetry_of_legal_moves():
+    # legal(pos) <-> legal(mirror(pos)) under the rank-mirror of the move strings (compare_policy.py:437-463)
+    for i in range(30):
+        pos = chesspos.playout(7, i, 60)[0]
+        a = sorted(vocab.mirror_uci(chesspos.uci(m)) for m in pos.legal_moves())
+        b = sorted(chesspos.uci(m) for m in pos.mirror().legal_moves())
+        assert a == b
