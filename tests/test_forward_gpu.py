@@ -293,3 +293,23 @@ def test_int8_w8a8_engine_tolerances(value_only):
         assert "policy" not in out
     print(msg)
     assert werr <= 3e-2
+
+
+def test_config1_shape_on_playout_positions_with_real_legal_masks():
+    """The 256-wide 8-layer encoder on 64 seeded random-playout positions (112-plane history input and legal
+    masks from the library's move generator) against the FP32 oracle: logits within 2e-2, WDL within 1e-2,
+    and the soft-maxed, masked policy puts exactly zero mass outside the legal moves."""
+    from chessrl_b200 import positions
+    cfg = bt4spec.SpecConfig.baseline(8, 256, 1024, 8, smolgen=False)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=41)
+    pos = positions.playout_positions(64, seed=20240607, max_plies=80)
+    tokens = pos["planes112"].float().view(64, 64, 112)
+    ref = oracle_out(cfg, sd, tokens)
+    out, eng = run_engine(cfg, sd, tokens)
+    assert (out["policy"] - ref["policy"]).abs().max() <= POLICY_TOL
+    assert (out["wdl"] - torch.softmax(ref["wdl"], -1)).abs().max() <= WDL_TOL
+    legal = torch.from_numpy(np.unpackbits(pos["legal1858"].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool))
+    probs = eng.forward(pos["planes112"].cuda(), legal_mask=pos["legal1858"].cuda(), policy_softmax=True)["policy"].cpu()
+    assert float(probs[~legal].max()) == 0.0 and torch.allclose(probs.sum(-1), torch.ones(64), atol=1e-4)
+    want = torch.softmax(bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal), -1)
+    assert (probs - want).abs().max() <= 1e-2
