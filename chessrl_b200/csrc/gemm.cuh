@@ -481,7 +481,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
+        if (PAIR && rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
         else mbar_arrive(tempty_bar(as));
       }
     }

@@ -90,7 +90,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (prm.out_dtype != kOutF32) {
     const int oesz = prm.out_dtype == kOutF16 ? 2 : 1;
     if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, 32 * oesz) == kOk)
-      prm.use_tma_store = 1;
+      prm.use_tma_store = getenv("CRL_NO_TMA_STORE") ? 0 : 1;
   }
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
   if constexpr (PAIR) {

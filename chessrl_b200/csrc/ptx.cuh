@@ -86,8 +86,11 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on an mbarrier of another CTA of the cluster. Relaxed: the barrier only hands a tensor-memory
+// buffer back (ordered by tcgen05.fence::before_thread_sync), no generic-memory data travels with it; a
+// cluster-scope release here was measured at ~2000 cycles per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
