@@ -313,3 +313,41 @@ def test_config1_shape_on_playout_positions_with_real_legal_masks():
     assert float(probs[~legal].max()) == 0.0 and torch.allclose(probs.sum(-1), torch.ones(64), atol=1e-4)
     want = torch.softmax(bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal), -1)
     assert (probs - want).abs().max() <= 1e-2
+
+
+def test_determinism_and_output_guards():
+    """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
+    outputs are carved out of larger buffers whose padding keeps its canary value."""
+    import ctypes
+    from chessrl_b200 import Engine, _lib as L, positions
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=51)
+    eng = Engine(engine_cfg(cfg, chunk=8))
+    eng.load_state_dict(sd)
+    b = 19                                                   # three chunks, the last one ragged
+    pos = positions.playout_positions(b, seed=3)
+    planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
+    stride = 1858 + 6
+    canary = 12345.0
+
+    def run():
+        policy = torch.full((b + 2, stride), canary, device="cuda")
+        wdl = torch.full((b + 2, 3), canary, device="cuda")
+        io = L.IO()
+        io.planes, io.layout, io.batch = planes.data_ptr(), L.LAYOUT_NHWC_F16, b
+        io.legal_mask, io.mask_mode, io.mask_stride = bits.data_ptr(), L.MASK_BITS, bits.shape[1]
+        io.policy_out, io.policy_dtype, io.policy_softmax, io.policy_stride = policy[1:].data_ptr(), L.OUT_F32, 1, stride
+        io.wdl_out, io.wdl_softmax = wdl[1:].data_ptr(), 1
+        ws = eng.workspace(b)
+        io.workspace, io.workspace_bytes = ws.data_ptr(), ws.numel()
+        io.stream = torch.cuda.current_stream().cuda_stream
+        assert eng.lib.crl_forward(eng._h, ctypes.byref(io)) == 0
+        torch.cuda.synchronize()
+        return policy.cpu(), wdl.cpu()
+
+    p1, w1 = run()
+    p2, w2 = run()
+    assert torch.equal(p1, p2) and torch.equal(w1, w2)
+    assert (p1[0] == canary).all() and (p1[-1] == canary).all() and (p1[1:-1, 1858:] == canary).all()
+    assert (w1[0] == canary).all() and (w1[-1] == canary).all()
+    assert torch.isfinite(p1[1:-1, :1858]).all() and torch.allclose(p1[1:-1, :1858].sum(-1), torch.ones(b), atol=1e-4)
