@@ -59,6 +59,8 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
   const long long stride = (long long)gridDim.x * NW;
   const uint32_t stage_bytes = 3u * 4096u + (p.has_bias == 1 ? 8192u : (p.has_bias == 2 ? 4096u : 0u));
   const int g = lane >> 2, t = lane & 3;
+  const uint32_t k_scale = pack_h2(p.scale * 1.4426950408889634f, p.scale * 1.4426950408889634f);
+  const uint32_t k_bias = pack_h2(p.bias_mult * 1.4426950408889634f, p.bias_mult * 1.4426950408889634f);
   int it = 0;
   for (long long item = first; item < items; item += stride, ++it) {
     const int board = static_cast<int>(item / p.H), h = static_cast<int>(item % p.H);
@@ -76,11 +78,15 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
     }
 
     for (int half = 0; half < 2; ++half) {
-      float s[2][8][4];
+      // Scores, softmax and probabilities live in packed f16 pairs: QK^T accumulates in f16 (32 products
+      // per score), the softmax runs in the log2 domain with one two-wide ex2 per pair of scores, and the
+      // probabilities are already in the A-fragment layout of the P.V product. The row sums come out of the
+      // same P.V product through an extra all-ones column of V (fp32 accumulation, no shuffles).
+      uint32_t sh[2][8][2];
 #pragma unroll
       for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int n = 0; n < 8; ++n) s[u][n][0] = s[u][n][1] = s[u][n][2] = s[u][n][3] = 0.0f;
+        for (int n = 0; n < 8; ++n) sh[u][n][0] = sh[u][n][1] = 0u;
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks) {
         uint32_t a[2][4];
@@ -94,94 +100,81 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
           ldsm_x4(sK + tile_off<32>(np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            mma16816(s[u][2 * np], a[u][0], a[u][1], a[u][2], a[u][3], b0, b1);
-            mma16816(s[u][2 * np + 1], a[u][0], a[u][1], a[u][2], a[u][3], b2, b3);
+            mma16816_h(sh[u][2 * np], a[u][0], a[u][1], a[u][2], a[u][3], b0, b1);
+            mma16816_h(sh[u][2 * np + 1], a[u][0], a[u][1], a[u][2], a[u][3], b2, b3);
           }
         }
       }
       float inv[2][2];
+      float o[2][5][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int n = 0; n < 5; ++n) o[u][n][0] = o[u][n][1] = o[u][n][2] = o[u][n][3] = 0.0f;
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int r0 = (half * 2 + u) * 16 + g;
+        // s2 = score * (scale * log2 e) + bias * (bias_mult * log2 e)
         if (p.has_bias == 1) {
-          // f16 tile, 128-byte rows, 128-byte swizzle: 16-byte chunk n of row r sits at chunk n ^ (r & 7)
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
-            const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(sB + r0 * 128 + ((n ^ (r0 & 7)) << 4) + 4 * t));
-            const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(sB + (r0 + 8) * 128 + ((n ^ ((r0 + 8) & 7)) << 4) + 4 * t));
-            s[u][n][0] = s[u][n][0] * p.scale + b0.x; s[u][n][1] = s[u][n][1] * p.scale + b0.y;
-            s[u][n][2] = s[u][n][2] * p.scale + b1.x; s[u][n][3] = s[u][n][3] * p.scale + b1.y;
+            const uint32_t ba = *reinterpret_cast<const uint32_t*>(sB + r0 * 128 + ((n ^ (r0 & 7)) << 4) + 4 * t);
+            const uint32_t bb = *reinterpret_cast<const uint32_t*>(sB + (r0 + 8) * 128 + ((n ^ ((r0 + 8) & 7)) << 4) + 4 * t);
+            sh[u][n][0] = hfma2_u32(sh[u][n][0], k_scale, hmul2_u32(ba, k_bias));
+            sh[u][n][1] = hfma2_u32(sh[u][n][1], k_scale, hmul2_u32(bb, k_bias));
           }
         } else if (p.has_bias == 2) {
-          // e4m3 tile, 64-byte rows, 64-byte swizzle
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
             const int ra = r0, rb = r0 + 8;
             const uint16_t wa = *reinterpret_cast<const uint16_t*>(sB + ra * 64 + (((n >> 1) ^ ((ra >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
             const uint16_t wb = *reinterpret_cast<const uint16_t*>(sB + rb * 64 + (((n >> 1) ^ ((rb >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
             const __half2_raw ha = __nv_cvt_fp8x2_to_halfraw2(wa, __NV_E4M3), hb = __nv_cvt_fp8x2_to_halfraw2(wb, __NV_E4M3);
-            const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&ha));
-            const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&hb));
-            s[u][n][0] = s[u][n][0] * p.scale + b0.x * p.bias_mult; s[u][n][1] = s[u][n][1] * p.scale + b0.y * p.bias_mult;
-            s[u][n][2] = s[u][n][2] * p.scale + b1.x * p.bias_mult; s[u][n][3] = s[u][n][3] * p.scale + b1.y * p.bias_mult;
+            sh[u][n][0] = hfma2_u32(sh[u][n][0], k_scale, hmul2_u32(*reinterpret_cast<const uint32_t*>(&ha), k_bias));
+            sh[u][n][1] = hfma2_u32(sh[u][n][1], k_scale, hmul2_u32(*reinterpret_cast<const uint32_t*>(&hb), k_bias));
           }
         } else {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s[u][n][j] *= p.scale;
+            sh[u][n][0] = hmul2_u32(sh[u][n][0], k_scale);
+            sh[u][n][1] = hmul2_u32(sh[u][n][1], k_scale);
           }
         }
-        float m0 = -INFINITY, m1 = -INFINITY;
+        // row maxima (rows r0 and r0+8; a row lives in the four lanes of a quad, two scores per register)
+        uint32_t m0 = sh[u][0][0], m1 = sh[u][0][1];
+#pragma unroll
+        for (int n = 1; n < 8; ++n) { m0 = hmax2_u32(m0, sh[u][n][0]); m1 = hmax2_u32(m1, sh[u][n][1]); }
+        m0 = hmax2_u32(m0, __byte_perm(m0, m0, 0x1032));
+        m1 = hmax2_u32(m1, __byte_perm(m1, m1, 0x1032));
+        m0 = hmax2_u32(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+        m0 = hmax2_u32(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+        m1 = hmax2_u32(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+        m1 = hmax2_u32(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
-          m0 = fmaxf(m0, fmaxf(s[u][n][0], s[u][n][1]));
-          m1 = fmaxf(m1, fmaxf(s[u][n][2], s[u][n][3]));
+          sh[u][n][0] = hexp2_u32(hsub2_u32(sh[u][n][0], m0));
+          sh[u][n][1] = hexp2_u32(hsub2_u32(sh[u][n][1], m1));
         }
-        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
-        m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
-        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
-        m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
-        float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          s[u][n][0] = __expf(s[u][n][0] - m0); s[u][n][1] = __expf(s[u][n][1] - m0);
-          s[u][n][2] = __expf(s[u][n][2] - m1); s[u][n][3] = __expf(s[u][n][3] - m1);
-          l0 += s[u][n][0] + s[u][n][1];
-          l1 += s[u][n][2] + s[u][n][3];
-        }
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-        inv[u][0] = 1.0f / l0; inv[u][1] = 1.0f / l1;
       }
-      float o[2][4][4];
-#pragma unroll
-      for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int n = 0; n < 4; ++n) o[u][n][0] = o[u][n][1] = o[u][n][2] = o[u][n][3] = 0.0f;
+      // O = P V, plus the all-ones column that yields the row sums
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        uint32_t a[2][4];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          a[u][0] = pack_h2(s[u][2 * kk][0], s[u][2 * kk][1]);
-          a[u][1] = pack_h2(s[u][2 * kk][2], s[u][2 * kk][3]);
-          a[u][2] = pack_h2(s[u][2 * kk + 1][0], s[u][2 * kk + 1][1]);
-          a[u][3] = pack_h2(s[u][2 * kk + 1][2], s[u][2 * kk + 1][3]);
-        }
 #pragma unroll
         for (int dp = 0; dp < 2; ++dp) {
           uint32_t b0, b1, b2, b3;
           ldsm_x4_t(sV + tile_off<32>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + ((lane >> 4) & 1)), b0, b1, b2, b3);
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            mma16816(o[u][2 * dp], a[u][0], a[u][1], a[u][2], a[u][3], b0, b1);
-            mma16816(o[u][2 * dp + 1], a[u][0], a[u][1], a[u][2], a[u][3], b2, b3);
+            mma16816(o[u][2 * dp], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], b0, b1);
+            mma16816(o[u][2 * dp + 1], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], b2, b3);
           }
         }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          mma16816(o[u][4], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], 0x3C003C00u, 0x3C003C00u);
       }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) { inv[u][0] = 1.0f / o[u][4][0]; inv[u][1] = 1.0f / o[u][4][2]; }
       // Every lane has taken its Q fragments of these two slabs: their rows now receive the context,
       // in the layout the store's tensor map swizzles.
       __syncwarp();
