@@ -298,7 +298,17 @@ def main():
     eng.profile(True)
     step()
     prof = eng.profile_read()
+    entries = eng.profile_entries()
     eng.profile(False)
+    # dominant kernel = the GEMM shape with the largest summed device time in the pass
+    shapes = {}
+    for e in entries:
+        if e["cat"] == 0:
+            acc = shapes.setdefault((e["m"], e["n"], e["k"], e["kind"]), [0, 0.0, 0.0])
+            acc[0] += 1
+            acc[1] += e["ms"]
+            acc[2] += e["flops"]
+    top_shape, top = max(shapes.items(), key=lambda kv: kv[1][1])
     peaks, peak_kind = measured_peaks()
     if dtype != crl.DTYPE_F16:
         lib_peak = fp8_library_peak(dev)
@@ -308,9 +318,19 @@ def main():
     else:
         peak, peak_note = peaks["bf16_tflops"], f"bf16_tflops, {peak_kind}"
     gm = prof["gemm"]
-    achieved = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
-    roofline = {"bound": "tensor", "kernel": "gemm_tn_kernel (tcgen05, all GEMMs of one pass)", "achieved": achieved,
-                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": None,
+    achieved = top[2] / (top[1] * 1e-3) / 1e12 if top[1] > 0 else 0.0
+    # DRAM bytes per launch from the ncu capture of this kernel and shape (profiles/): 137.5 MB read + 752.9 MB
+    # written at M = 131072, N = 3072, K = 1024, e4m3; A and C scale with M
+    traffic = None
+    if top_shape[1:] == (3072, 1024, 1):
+        traffic = int(890.4e6 * top_shape[0] / 131072)
+    all_gemm = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
+    roofline = {"bound": "tensor",
+                "kernel": "gemm_tn_kernel<256,%s,pair> M=%d N=%d K=%d (the GEMM shape with the largest share of the pass)"
+                          % (("f16", "e4m3", "int8")[top_shape[3]], top_shape[0], top_shape[1], top_shape[2]),
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
+                "traffic": traffic, "algorithmic_flops_per_launch": top[2] / top[0], "launches_in_pass": top[0],
+                "avg_launch_ms": top[1] / top[0], "all_gemms_achieved": all_gemm,
                 "peak_source": peak_note, "launches": gm["launches"], "ms_per_step": gm["ms"],
                 "share_of_step": gm["ms"] / sum(v["ms"] for v in prof.values()) if gm["ms"] else None,
                 "whole_forward_frac": value * fpp / 1e12 / world / peak if peak else None,

@@ -31,8 +31,8 @@ struct LayerW {
   __half *sg_wc = nullptr, *sg_w1 = nullptr, *sg_w2 = nullptr;
   float *sg_b1 = nullptr, *sg_b2 = nullptr, *sg_ln1w = nullptr, *sg_ln1b = nullptr, *sg_ln2w = nullptr, *sg_ln2b = nullptr;
   // FP8: e4m3 weights, the multipliers they were quantised with, and the activation multipliers
-  uint8_t *wqkv8 = nullptr, *wo8 = nullptr, *wff1_8 = nullptr, *wff2_8 = nullptr;
-  float sw_qkv = 1, sw_o = 1, sw_ff1 = 1, sw_ff2 = 1;
+  uint8_t *wqkv8 = nullptr, *wo8 = nullptr, *wff1_8 = nullptr, *wff2_8 = nullptr, *sg_wc8 = nullptr;
+  float sw_qkv = 1, sw_o = 1, sw_ff1 = 1, sw_ff2 = 1, sw_c = 1;
   // INT8: per-output-channel symmetric weights and their scales
   int8_t *wqkv_q = nullptr, *wo_q = nullptr, *wff1_q = nullptr, *wff2_q = nullptr;
   float *cs_qkv = nullptr, *cs_o = nullptr, *cs_ff1 = nullptr, *cs_ff2 = nullptr;
@@ -467,6 +467,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     if (c.bias_mode == CRL_BIAS_SMOLGEN) {
       const int cc = c.smolgen_compress, hid = c.smolgen_hidden, gen = c.smolgen_gen;
       Lin a; a.a = attn_in; a.lda = d; a.w = L.sg_wc; a.ldw = d; a.c = w.sg_c; a.ldc = cc; a.m = M; a.n = cc; a.k = d;
+      // FP8 engine: this projection is a pure read of the token rows, so it takes the e4m3 copy (half the bytes)
+      if (f8) { a.kind = kKindF8; a.a = attn_in8; a.w = L.sg_wc8; a.alpha = 1.0f / (L.sa_in * L.sw_c); }
       if ((rc = linear(h, a, s)) != CRL_OK) return rc;
       Lin b; b.a = w.sg_c; b.lda = 64 * cc; b.w = L.sg_w1; b.ldw = 64 * cc; b.c = w.sg_h1; b.ldc = hid; b.m = bc; b.n = hid;
       b.k = 64 * cc; b.bias = L.sg_b1; b.act = act;
@@ -950,6 +952,10 @@ int crl_finalize(crl_handle* h) {
       if ((rc = upload_e4m3(h, &L.wo8, &L.sw_o, wo.data(), wo.size())) != CRL_OK) return rc;
       if ((rc = upload_e4m3(h, &L.wff1_8, &L.sw_ff1, w1.data(), w1.size())) != CRL_OK) return rc;
       if ((rc = upload_e4m3(h, &L.wff2_8, &L.sw_ff2, w2.data(), w2.size())) != CRL_OK) return rc;
+      if (c.bias_mode == CRL_BIAS_SMOLGEN) {
+        const auto& wc = *get(h, lkey(l, "smolgen.compress.weight"));
+        if ((rc = upload_e4m3(h, &L.sg_wc8, &L.sw_c, wc.data(), wc.size())) != CRL_OK) return rc;
+      }
     }
   }
   if (c.bias_mode == CRL_BIAS_SMOLGEN) UP16(h->sg_shared, "smolgen_shared.weight", 4096, c.smolgen_gen, c.smolgen_gen);
