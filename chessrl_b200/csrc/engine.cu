@@ -330,7 +330,13 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
   p.yq = yq; p.yq_scale = yq_scale;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * d * (2 + (y != nullptr ? 2 : 0) + (y8 != nullptr ? 1 : 0)));
-  ln_rows_kernel<<<blocks, 256, 0, s>>>(p);
+  if (yq == nullptr && gate_ea == nullptr && rows >= 8192) {
+    const long long want = (rows + 7) / 8;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 2));
+    ln_rows_persistent_kernel<<<grid, 256, 0, s>>>(p);
+  } else {
+    ln_rows_kernel<<<blocks, 256, 0, s>>>(p);
+  }
   CRL_CUDA(h, cudaGetLastError());
   ++h->launches;
   return CRL_OK;

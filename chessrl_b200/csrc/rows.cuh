@@ -180,6 +180,94 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
   }
 }
 
+// The per-layer LayerNorms (no gating, no int8): persistent warps walk rows grid-stride with the affine
+// parameters of their own columns held in registers as f16 pairs. The plain kernel above re-reads weight and
+// bias through L1 for every row (four times the bytes of the row itself), which made L1 throughput, not HBM,
+// its limit; here a row costs one 16-byte load and at most two stores per lane and vector.
+__global__ void __launch_bounds__(256) ln_rows_persistent_kernel(const LnParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int NV = 4;
+  const long long stride = (long long)gridDim.x * 8;
+  long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= p.rows) return;
+  uint32_t wh[NV][4], bh[NV][4];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool ok = c < p.d;
+      const __half2 w2 = __floats2half2_rn(ok ? p.w[c + 2 * j] : 0.0f, ok ? p.w[c + 2 * j + 1] : 0.0f);
+      const __half2 b2 = __floats2half2_rn(ok ? p.b[c + 2 * j] : 0.0f, ok ? p.b[c + 2 * j + 1] : 0.0f);
+      wh[i][j] = *reinterpret_cast<const uint32_t*>(&w2);
+      bh[i][j] = *reinterpret_cast<const uint32_t*>(&b2);
+    }
+  }
+  uint4 raw[NV], nxt[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    raw[i] = c < p.d ? *reinterpret_cast<const uint4*>(p.x + row * p.ldx + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const __half2 s8 = __floats2half2_rn(p.out8_scale, p.out8_scale);
+  for (; row < p.rows; row += stride) {
+    const long long nrow = row + stride;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      nxt[i] = (nrow < p.rows && c < p.d) ? *reinterpret_cast<const uint4*>(p.x + nrow * p.ldx + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float sum = 0.0f, sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        sum += f.x + f.y;
+        sq = fmaf(f.x, f.x, fmaf(f.y, f.y, sq));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    }
+    const float mean = sum / p.d;
+    const float rstd = rsqrtf(fmaxf(sq / p.d - mean * mean, 0.0f) + 1e-5f);
+    const float shift = -mean * rstd;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < p.d) {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+        uint32_t o16[4];
+        __half2 y2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
+          y2[j] = __hfma2(xn, *reinterpret_cast<const __half2*>(&wh[i][j]), *reinterpret_cast<const __half2*>(&bh[i][j]));
+          o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
+        }
+        if (p.y != nullptr) *reinterpret_cast<uint4*>(p.y + row * p.ldy + c) = make_uint4(o16[0], o16[1], o16[2], o16[3]);
+        if (p.y8 != nullptr) {
+          uint32_t w8[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+            w8[j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                    (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+          }
+          *reinterpret_cast<uint2*>(p.y8 + row * p.ldy8 + c) = make_uint2(w8[0], w8[1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[i] = nxt[i];
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Value-head tail (new_paradigm/value.py:427-435 last layer + the softmax of value.py:271):
 // in [B,128] f16 -> Linear(128 -> n_out) -> mode 0 raw / 1 softmax / 2 tanh -> out [B, n_out] f32.
