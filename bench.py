@@ -193,6 +193,8 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="global positions per step (default: the workload's)")
     ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--input", default="packed104", choices=["packed104", "f16"],
+                    help="input planes: 840-byte bit-packed records expanded on the device, or [B,8,8,112] f16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-latency", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="config 5 batch sweep (1..16384) of INT8 against FP16")
@@ -209,7 +211,9 @@ def main():
     config = {"workload": f"{args.workload}: BT4-shaped encoder d{d} L{L} H{H} ff{ff}" + (" smolgen" if wl["smolgen"] else "") +
                           f" gather-policy-1858+mask+softmax WDL, {wl['dtype']}, {wl['batch']} positions/step",
               "global_batch": wl["batch"], "parallelism": f"replicas x{world} (positions sharded, weights replicated)",
-              "l2": "activations per pass exceed the 126 MB L2; no flush needed", "flop_per_position": fpp}
+              "l2": "activations per pass exceed the 126 MB L2; no flush needed", "flop_per_position": fpp,
+              "input": "bit-packed 840-byte records (104 bitboards + 8 bytes), expanded on the device" if args.input == "packed104"
+                       else "[B,8,8,112] f16 planes"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -246,15 +250,19 @@ def main():
     from chessrl_b200 import positions
     pos = positions.playout_positions(per_rank, seed=20240607, first=rank * per_rank, max_plies=80, pin_memory=True)
     planes_host, bits_host = pos["planes112"], pos["legal1858"]
+    layout = "nhwc"
+    if args.input == "packed104":
+        planes_host, layout = positions.pack_planes104(planes_host, pin_memory=True), "packed104"
     planes, bits = planes_host.to(dev), bits_host.to(dev)
     if dtype == crl.DTYPE_F8E4M3:
-        eng.calibrate(planes[: min(per_rank, 2048)])
+        eng.calibrate(planes[: min(per_rank, 2048)], layout=layout)
 
     def step():
-        return eng.forward(planes, legal_mask=None if value_only else bits, policy_softmax=True, policy_dtype=torch.float16)
+        return eng.forward(planes, layout=layout, legal_mask=None if value_only else bits, policy_softmax=True,
+                           policy_dtype=torch.float16)
 
     def step_host():
-        return eng.forward(planes_host, legal_mask=None if value_only else bits_host, policy_softmax=True,
+        return eng.forward(planes_host, layout=layout, legal_mask=None if value_only else bits_host, policy_softmax=True,
                            policy_dtype=torch.float16, host=True)
 
     def barrier():
@@ -291,7 +299,7 @@ def main():
     step_host()
     ms_e2e = timed(step_host, args.steps) / args.steps
     e2e = {"value": wl["batch"] / (ms_e2e * 1e-3), "unit": "positions/s",
-           "h2d_bytes_per_step": (planes_host.numel() * 2 + bits_host.numel()) * world,
+           "h2d_bytes_per_step": (planes_host.numel() * planes_host.element_size() + bits_host.numel()) * world,
            "d2h_bytes_per_step": ((0 if value_only else per_rank * 1858 * 2) + per_rank * 12) * world}
 
     # per-kernel pass (untimed): CUDA events around every launch, on the launch stream
@@ -349,13 +357,13 @@ def main():
             for bsz in (1, 16, 256, 4096, 16384):
                 pl = planes[:bsz]
                 for _ in range(3):
-                    e2.forward(pl, policy=not value_only)
+                    e2.forward(pl, layout=layout, policy=not value_only)
                 torch.cuda.synchronize()
                 reps = 20 if bsz <= 256 else 3
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 for _ in range(reps):
-                    e2.forward(pl, policy=not value_only)
+                    e2.forward(pl, layout=layout, policy=not value_only)
                 e1.record()
                 torch.cuda.synchronize()
                 sweep[name][str(bsz)] = bsz / (e0.elapsed_time(e1) / reps * 1e-3)

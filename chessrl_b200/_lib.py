@@ -17,7 +17,8 @@ BIAS_NONE, BIAS_CAUSAL, BIAS_RELPOS, BIAS_SMOLGEN = 0, 1, 2, 3
 POLICY_NONE, POLICY_DENSE4096, POLICY_GATHER1858, POLICY_LM_HEAD = 0, 1, 2, 3
 VALUE_NONE, VALUE_WDL, VALUE_WDL_Q = 0, 1, 2
 DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8 = 0, 1, 2
-LAYOUT_NHWC_F32, LAYOUT_NHWC_F16, LAYOUT_NCHW_F16, LAYOUT_NCHW_F32 = 0, 1, 2, 3
+LAYOUT_NHWC_F32, LAYOUT_NHWC_F16, LAYOUT_NCHW_F16, LAYOUT_NCHW_F32, LAYOUT_PACKED104 = 0, 1, 2, 3, 4
+PACKED104_BYTES = 840
 MASK_NONE, MASK_BITS, MASK_ADDITIVE = 0, 1, 2
 OUT_F32, OUT_F16 = 0, 1
 VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
@@ -27,7 +28,7 @@ EXPORTS = [
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
     "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static", "crl_perft", "crl_fen_to_planes19", "crl_legal_mask_1929",
-    "crl_playout_positions",
+    "crl_playout_positions", "crl_pack_planes104",
 ]
 
 
@@ -118,6 +119,8 @@ def load():
     lib.crl_legal_mask_1929.restype = ctypes.c_int
     lib.crl_playout_positions.argtypes = [ctypes.c_uint64, i64, i64, i32, i32, vp, vp, vp, vp, vp, vp]
     lib.crl_playout_positions.restype = ctypes.c_int
+    lib.crl_pack_planes104.argtypes = [vp, i32, i64, vp]
+    lib.crl_pack_planes104.restype = ctypes.c_int
     lib.crl_vocab_move.argtypes = [ctypes.c_int, ctypes.c_char_p]
     lib.crl_vocab_move.restype = ctypes.c_int
     lib.crl_vocab_mirror_index.argtypes = [ctypes.c_int]

@@ -424,6 +424,61 @@ int crl_legal_mask_1929(const char* fen, uint8_t* bits) {
   return CRL_OK;
 }
 
+int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_t* packed) {
+  if (count < 0 || (count > 0 && (planes == nullptr || packed == nullptr))) return CRL_ERR_INVALID;
+  if (layout != CRL_LAYOUT_NHWC_F16 && layout != CRL_LAYOUT_NHWC_F32) return CRL_ERR_INVALID;
+  const bool f32 = layout == CRL_LAYOUT_NHWC_F32;
+  // Every representable value is identified by its bit pattern: 0, 1, and c/100 for plane 109.
+  auto bits_of = [&](float v) -> uint32_t {
+    if (!f32) return f32_to_f16(v);
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    return u;
+  };
+  const uint32_t zero = bits_of(0.0f), one = bits_of(1.0f);
+  uint32_t clock_bits[101];
+  for (int c = 0; c <= 100; ++c) clock_bits[c] = bits_of(std::min(c / 100.0f, 1.0f));
+  for (int64_t i = 0; i < count; ++i) {
+    uint8_t* rec = packed + i * CRL_PACKED104_BYTES;
+    std::memset(rec, 0, CRL_PACKED104_BYTES);
+    auto at = [&](int s, int p) -> uint32_t {
+      const size_t k = (static_cast<size_t>(i) * 64 + s) * 112 + p;
+      if (f32) {
+        uint32_t u;
+        std::memcpy(&u, static_cast<const float*>(planes) + k, 4);
+        return u == 0x80000000u ? 0u : u;                       // -0.0 counts as empty
+      }
+      const uint16_t h = static_cast<const uint16_t*>(planes)[k];
+      return h == 0x8000u ? 0u : h;
+    };
+    for (int p = 0; p < 104; ++p)
+      for (int s = 0; s < 64; ++s) {
+        const uint32_t v = at(s, p);
+        if (v == one) rec[p * 8 + (s >> 3)] |= static_cast<uint8_t>(0x80u >> (s & 7));
+        else if (v != zero) return CRL_ERR_INVALID;
+      }
+    for (int p = 104; p < 112; ++p) {
+      const uint32_t v = at(0, p);
+      for (int s = 1; s < 64; ++s)
+        if (at(s, p) != v) return CRL_ERR_INVALID;              // auxiliary planes are constant over the board
+      if (p <= 108) {
+        if (v != zero && v != one) return CRL_ERR_INVALID;
+        rec[832 + (p - 104)] = v == one ? 1 : 0;
+      } else if (p == 109) {
+        int c = 0;
+        while (c <= 100 && clock_bits[c] != v) ++c;
+        if (c > 100) return CRL_ERR_INVALID;
+        rec[837] = static_cast<uint8_t>(c);
+      } else if (p == 110) {
+        if (v != zero) return CRL_ERR_INVALID;
+      } else if (v != one) {
+        return CRL_ERR_INVALID;
+      }
+    }
+  }
+  return CRL_OK;
+}
+
 int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t max_plies, int32_t rule50_plane,
                           uint16_t* planes112_f16, float* planes19_f32, uint8_t* legal1858, uint8_t* legal1929,
                           uint8_t* black, char* fens) {

@@ -431,6 +431,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
         tokens_from_nchw_kernel<__half><<<static_cast<unsigned>(bc), 256, smem, s>>>(static_cast<const __half*>(io->planes) + b0 * per_pos, w.xin, P, h->ppad);
       else
         tokens_from_nchw_kernel<float><<<static_cast<unsigned>(bc), 256, smem, s>>>(static_cast<const float*>(io->planes) + b0 * per_pos, w.xin, P, h->ppad);
+    } else if (io->layout == CRL_LAYOUT_PACKED104) {
+      tokens_from_packed104_kernel<<<static_cast<unsigned>(bc), 256, 0, s>>>(static_cast<const uint8_t*>(io->planes) + b0 * CRL_PACKED104_BYTES, w.xin, h->ppad);
     } else {
       return fail(h, CRL_ERR_INVALID, "unknown plane layout");
     }
@@ -648,7 +650,9 @@ int check_io(crl_handle* h, const crl_io* io) {
   if (!h->finalized) return fail(h, CRL_ERR_NOT_FINALIZED, "crl_finalize has not run");
   if (io->batch < 0) return fail(h, CRL_ERR_INVALID, "negative batch");
   if (io->batch > 0 && io->planes == nullptr) return fail(h, CRL_ERR_INVALID, "planes is null");
-  if (io->layout < 0 || io->layout > 3) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
+  if (io->layout < 0 || io->layout > CRL_LAYOUT_PACKED104) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
+  if (io->layout == CRL_LAYOUT_PACKED104 && h->cfg.planes != 112) return fail(h, CRL_ERR_INVALID, "the packed layout holds 112 planes");
+  if (io->layout == CRL_LAYOUT_PACKED104 && (reinterpret_cast<uintptr_t>(io->planes) & 3) != 0) return fail(h, CRL_ERR_INVALID, "packed planes must be 4-byte aligned");
   if (io->mask_mode < 0 || io->mask_mode > 2) return fail(h, CRL_ERR_INVALID, "unknown mask mode");
   const int n_moves = crl_num_moves(h);
   if (io->policy_out != nullptr) {
@@ -704,6 +708,7 @@ int grow(crl_handle* h, T** p, size_t* have, size_t need) {
 }
 
 size_t plane_bytes(const crl_handle* h, int layout) {
+  if (layout == CRL_LAYOUT_PACKED104) return CRL_PACKED104_BYTES;
   const size_t e = (layout == CRL_LAYOUT_NHWC_F32 || layout == CRL_LAYOUT_NCHW_F32) ? 4 : 2;
   return static_cast<size_t>(64) * h->cfg.planes * e;
 }
@@ -1023,7 +1028,7 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
                   size_t workspace_bytes, void* stream) {
   if (h == nullptr || planes == nullptr || batch <= 0) return CRL_ERR_INVALID;
   if (!h->finalized) return fail(h, CRL_ERR_NOT_FINALIZED, "crl_finalize has not run");
-  if (layout < 0 || layout > 3) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
+  if (layout < 0 || layout > CRL_LAYOUT_PACKED104) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
   CRL_CUDA(h, cudaSetDevice(h->device));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int L = h->cfg.n_layers;

@@ -51,6 +51,37 @@ __global__ void tokens_from_nchw_kernel(const TIn* __restrict__ in, __half* __re
   }
 }
 
+// One block per position: a 840-byte packed record (104 bit planes + 8 auxiliary bytes; byte r of a plane =
+// rank r, bit 7-f = file f) -> [64][ldo] f16 token rows, columns [112, ldo) zero. The record is staged in
+// shared memory; each thread then builds 16-byte pieces (8 planes of one token) from it.
+__global__ void __launch_bounds__(256) tokens_from_packed104_kernel(const uint8_t* __restrict__ in,
+                                                                    __half* __restrict__ out, int ldo) {
+  __shared__ __align__(16) uint8_t rec[848];
+  const long long b = blockIdx.x;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(in + b * 840);   // 840 = 4 * 210: word-aligned
+  for (int i = threadIdx.x; i < 210; i += blockDim.x) reinterpret_cast<uint32_t*>(rec)[i] = src[i];
+  __syncthreads();
+  const int chunks = ldo / 8;
+  const __half one = __float2half_rn(1.0f), zero = __float2half_rn(0.0f);
+  __half* dst = out + b * 64 * ldo;
+  for (int i = threadIdx.x; i < 64 * chunks; i += blockDim.x) {
+    const int tok = i / chunks, c0 = (i % chunks) * 8;
+    const int byte = tok >> 3, bit = 7 - (tok & 7);
+    __align__(16) __half h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int p = c0 + j;
+      __half v = zero;
+      if (p < 104) v = ((rec[p * 8 + byte] >> bit) & 1) ? one : zero;
+      else if (p < 109) v = rec[832 + (p - 104)] ? one : zero;
+      else if (p == 109) v = __float2half_rn(fminf(static_cast<float>(rec[837]) / 100.0f, 1.0f));
+      else if (p == 111) v = one;
+      h[j] = v;
+    }
+    *reinterpret_cast<uint4*>(dst + tok * ldo + c0) = *reinterpret_cast<const uint4*>(h);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // LayerNorm over rows of up to 1024 f16 elements (eps 1e-5, affine), one warp per row.
 //   y = LN(x) * w + b ; optional gating y = y * ea[token] + gb[token] (token = row % 64; ea = exp(a),

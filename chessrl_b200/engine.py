@@ -63,6 +63,7 @@ class EngineConfig:
 _LAYOUT_OF = {
     ("nhwc", torch.float32): L.LAYOUT_NHWC_F32, ("nhwc", torch.float16): L.LAYOUT_NHWC_F16,
     ("nchw", torch.float16): L.LAYOUT_NCHW_F16, ("nchw", torch.float32): L.LAYOUT_NCHW_F32,
+    ("packed104", torch.uint8): L.LAYOUT_PACKED104,
 }
 
 
@@ -128,6 +129,10 @@ class Engine:
 
     def _batch_of(self, planes, layout):
         p = self.cfg.planes
+        if layout == "packed104":
+            if planes.dim() != 2 or planes.shape[1] != L.PACKED104_BYTES:
+                raise ValueError(f"packed planes are [B, {L.PACKED104_BYTES}] uint8")
+            return planes.shape[0]
         if planes.numel() % (64 * p) != 0:
             raise ValueError("planes tensor is not a whole number of positions")
         if layout == "nhwc" and planes.shape[-1] != p:
@@ -147,7 +152,8 @@ class Engine:
     def forward(self, planes, layout="nhwc", legal_mask=None, mask_mode=None, policy=True, wdl=True, q=False,
                 policy_softmax=False, wdl_softmax=True, policy_dtype=torch.float32, host=False, rl_vocab=False,
                 black_rows=None):
-        """planes: [..., 8, 8, P] ("nhwc") or [B, P, 8, 8] ("nchw"), on the engine's GPU (or on the host
+        """planes: [..., 8, 8, P] ("nhwc"), [B, P, 8, 8] ("nchw") or [B, 840] uint8 bit-packed records
+        ("packed104", see positions.pack_planes104), on the engine's GPU (or on the host
         with host=True, which times like a user call: copies in, run, copies out, synchronise).
         legal_mask: uint8 bitset [B, ceil(V/8)] (bit m of row b: move m legal) or float32 additive [B, V].
         rl_vocab=True (gather head): rows of 1929 in the reference's own vocabulary, Black rows (uint8 flags in

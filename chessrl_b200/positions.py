@@ -62,3 +62,22 @@ def playout_positions(count, seed=20240607, first=0, max_plies=80, rule50_plane=
     if fens:
         out["fens"] = [fbuf.raw[i * 96:(i + 1) * 96].split(b"\0", 1)[0].decode() for i in range(count)]
     return out
+
+
+def pack_planes104(planes, pin_memory=False):
+    """[..., 8, 8, 112] f16/f32 host planes (token-major, as `playout_positions` yields them) -> [B, 840] uint8
+    records of the "packed104" input layout: 104 bit planes in the byte/bit order of the lc0 training record
+    (LeelaData/show_value_head_ground_truth.py:58-88) followed by castling, side-to-move and half-move-clock bytes.
+    17 times fewer bytes to move to the GPU than f16 planes; the engine expands them on the device."""
+    planes = planes.contiguous()
+    if planes.device.type != "cpu" or planes.shape[-1] != 112 or planes.numel() % (64 * 112) != 0:
+        raise ValueError("expected host planes [..., 8, 8, 112]")
+    layout = {torch.float16: L.LAYOUT_NHWC_F16, torch.float32: L.LAYOUT_NHWC_F32}.get(planes.dtype)
+    if layout is None:
+        raise ValueError("planes must be float16 or float32")
+    count = planes.numel() // (64 * 112)
+    out = torch.empty(count, L.PACKED104_BYTES, dtype=torch.uint8, pin_memory=pin_memory)
+    rc = L.load().crl_pack_planes104(planes.data_ptr(), layout, count, out.data_ptr())
+    if rc != 0:
+        raise L.CrlError(rc, "pack_planes104: a plane is not representable (piece planes 0/1, constant auxiliary planes)")
+    return out

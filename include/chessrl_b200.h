@@ -39,7 +39,18 @@ enum { CRL_BIAS_NONE = 0, CRL_BIAS_CAUSAL = 1, CRL_BIAS_RELPOS = 2, CRL_BIAS_SMO
 enum { CRL_POLICY_NONE = 0, CRL_POLICY_DENSE4096 = 1, CRL_POLICY_GATHER1858 = 2, CRL_POLICY_LM_HEAD = 3 };
 enum { CRL_VALUE_NONE = 0, CRL_VALUE_WDL = 1, CRL_VALUE_WDL_Q = 2 };
 enum { CRL_DTYPE_F16 = 0, CRL_DTYPE_F8E4M3 = 1, CRL_DTYPE_I8 = 2 };
-enum { CRL_LAYOUT_NHWC_F32 = 0, CRL_LAYOUT_NHWC_F16 = 1, CRL_LAYOUT_NCHW_F16 = 2, CRL_LAYOUT_NCHW_F32 = 3 };
+enum { CRL_LAYOUT_NHWC_F32 = 0, CRL_LAYOUT_NHWC_F16 = 1, CRL_LAYOUT_NCHW_F16 = 2, CRL_LAYOUT_NCHW_F32 = 3,
+       CRL_LAYOUT_PACKED104 = 4 };
+/* CRL_LAYOUT_PACKED104 (112-plane networks only): CRL_PACKED104_BYTES per position, the plane block of the lc0
+ * training record as the reference reads it (LeelaData/show_value_head_ground_truth.py:58-88,191-203):
+ *   bytes [0,832)  104 planes x 8 bytes; byte r of a plane = rank r as seen by the side to move (r 0 = its first
+ *                  rank), bit (7 - f) of that byte = file f (the order numpy.unpackbits yields);
+ *   byte 832..835  castling rights: ours O-O-O, ours O-O, theirs O-O-O, theirs O-O  -> planes 104..107;
+ *   byte 836       non-zero = Black to move                                          -> plane 108;
+ *   byte 837       half-move clock c, plane 109 = min(c/100, 1) (0 for networks without that plane);
+ *   byte 838, 839  ignored (plane 110 is empty, plane 111 is all ones).
+ * The library expands it on the device into the token rows of the embedding GEMM. */
+#define CRL_PACKED104_BYTES 840
 enum { CRL_MASK_NONE = 0, CRL_MASK_BITS = 1, CRL_MASK_ADDITIVE = 2 };
 enum { CRL_OUT_F32 = 0, CRL_OUT_F16 = 1 };
 enum { CRL_VOCAB_NATIVE = 0, CRL_VOCAB_RL1929 = 1 };
@@ -198,6 +209,13 @@ int crl_legal_mask_1929(const char* fen, uint8_t* bits);
 int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t max_plies, int32_t rule50_plane,
                           uint16_t* planes112_f16, float* planes19_f32, uint8_t* legal1858, uint8_t* legal1929,
                           uint8_t* black, char* fens);
+
+/* Packs `count` positions of 112 planes in token-major order ([count,64,112]; layout CRL_LAYOUT_NHWC_F16 or
+ * CRL_LAYOUT_NHWC_F32, host memory) into CRL_LAYOUT_PACKED104 records. CRL_ERR_INVALID when a plane cannot be
+ * represented: a piece plane holding something other than 0/1, an auxiliary plane that is not constant over
+ * the board, a plane-109 value that is not min(c/100, 1) for an integer c, plane 110 not empty or plane 111
+ * not all ones. */
+int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_t* packed);
 
 /* Move vocabulary (utils/vocab.py:9-438): writes the UCI string of entry `index` of the 1929-entry
  * list into buf (>= 16 bytes); entries < 1858 are the Leela list. Returns 0, or CRL_ERR_INVALID. */

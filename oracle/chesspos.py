@@ -289,3 +289,37 @@ def playout(seed, index, max_plies):
         pos = Position()
         hist = [pos.copy()]
     return hist[::-1][:8]
+
+
+def unpack_planes104(packed):
+    """Test oracle for the "packed104" input layout: [B, 840] uint8 -> [B, 64, 112] float32 token-major planes.
+    Bit order as the reference reads the lc0 record (LeelaData/show_value_head_ground_truth.py:70-86:
+    `np.unpackbits` over the 8 bytes of a plane, square = 8*row + col), auxiliary bytes at the offsets of
+    show_value_head_ground_truth.py:191-197 relative to the plane block (us_ooo, us_oo, them_ooo, them_oo,
+    side to move, rule50 count)."""
+    import numpy as np
+    packed = np.asarray(packed, dtype=np.uint8)
+    B = packed.shape[0]
+    out = np.zeros((B, 64, 112), dtype=np.float32)
+    bits = np.unpackbits(packed[:, :832], axis=1).reshape(B, 104, 64)
+    out[:, :, :104] = bits.transpose(0, 2, 1)
+    for k in range(4):
+        out[:, :, 104 + k] = (packed[:, 832 + k] != 0)[:, None]
+    out[:, :, 108] = (packed[:, 836] != 0)[:, None]
+    out[:, :, 109] = np.minimum(packed[:, 837].astype(np.float32) / np.float32(100.0), np.float32(1.0))[:, None]
+    out[:, :, 111] = 1.0
+    return out
+
+
+def pack_planes104(planes):
+    """Inverse of `unpack_planes104` for representable planes ([B, 64, 112] float array) - numpy restatement used
+    to cross-check the library's packer."""
+    import numpy as np
+    planes = np.asarray(planes, dtype=np.float32).reshape(-1, 64, 112)
+    B = planes.shape[0]
+    rec = np.zeros((B, 840), dtype=np.uint8)
+    rec[:, :832] = np.packbits(planes[:, :, :104].transpose(0, 2, 1).reshape(B, 104 * 64) != 0, axis=1)
+    for k in range(5):
+        rec[:, 832 + k] = planes[:, 0, 104 + k] != 0
+    rec[:, 837] = np.rint(planes[:, 0, 109].astype(np.float64) * 100.0).astype(np.uint8)
+    return rec

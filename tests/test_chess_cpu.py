@@ -79,3 +79,54 @@ def test_mirror_symmetry_of_legal_moves():
         a = sorted(vocab.mirror_uci(chesspos.uci(m)) for m in pos.legal_moves())
         b = sorted(chesspos.uci(m) for m in pos.mirror().legal_moves())
         assert a == b
+
+
+def test_packed104_records_round_trip_and_reject_unrepresentable_planes(lib):
+    """The bit-packed input records: library packer == the oracle's numpy packer byte for byte, the oracle's
+    reading of the records (the bit order of the reference's lc0-record reader) gives back the planes exactly,
+    the piece of the record the reference decodes (first 12 planes -> board) is the position's own board, and
+    planes that cannot be represented are refused."""
+    import torch
+    from chessrl_b200 import positions, CrlError
+    n = 300
+    got = positions.playout_positions(n, seed=7, max_plies=120, fens=True)
+    planes = got["planes112"]
+    rec = positions.pack_planes104(planes)
+    assert rec.shape == (n, 840) and rec.dtype == torch.uint8
+    ref = planes.float().numpy().reshape(n, 64, 112)
+    np.testing.assert_array_equal(rec.numpy(), chesspos.pack_planes104(ref))
+    back = chesspos.unpack_planes104(rec.numpy())
+    np.testing.assert_array_equal(back.astype(np.float16).astype(np.float32), ref)
+    # the reference's reader: unpackbits over the first 96 bytes, square = 8*row + col, "PNBRQKpnbrqk"
+    for i in range(0, n, 17):
+        bits = np.unpackbits(rec[i, :96].numpy()).reshape(12, 64)
+        board = [["." for _ in range(8)] for _ in range(8)]
+        for k, ch in enumerate("PNBRQKpnbrqk"):
+            for sq in np.nonzero(bits[k])[0]:
+                board[7 - sq // 8][sq % 8] = ch
+        pos = chesspos.Position(got["fens"][i])
+        view = pos.mirror() if pos.turn == chesspos.BLACK else pos
+        want = view.fen().split()[0]
+        rows = []
+        for r in board:
+            out, run = "", 0
+            for ch in r:
+                if ch == ".":
+                    run += 1
+                else:
+                    out += (str(run) if run else "") + ch
+                    run = 0
+            rows.append(out + (str(run) if run else ""))
+        assert "/".join(rows) == want
+        assert int(rec[i, 836]) == int(got["black"][i])
+    # empty and ragged inputs, then planes with no packed form
+    assert positions.pack_planes104(planes[:0]).shape == (0, 840)
+    assert torch.equal(positions.pack_planes104(planes[5:6]), rec[5:6])
+    for plane, tok, val in [(3, 10, 0.5), (104, 7, 1.0 - float(planes[0, 0, 7, 104])), (110, 0, 1.0), (111, 63, 0.0), (109, 1, 0.123)]:
+        bad = planes[:2].clone()
+        bad.view(2, 64, 112)[1, tok, plane] = val
+        with pytest.raises(CrlError):
+            positions.pack_planes104(bad)
+    f32_exact = planes[:4].float()
+    f32_exact.view(4, 64, 112)[:, :, 109] = torch.tensor([0.0, 0.07, 0.5, 1.0]).view(4, 1)
+    assert positions.pack_planes104(f32_exact)[:, 837].tolist() == [0, 7, 50, 100]

@@ -315,6 +315,39 @@ def test_config1_shape_on_playout_positions_with_real_legal_masks():
     assert (probs - want).abs().max() <= 1e-2
 
 
+def test_packed104_input_is_bit_identical_to_f16_planes():
+    """The 840-byte bit-packed records expanded on the device give the same token rows as the f16 planes they
+    were packed from: policy and WDL are bit-identical, through the device call (two chunks + a ragged tail),
+    the host call and the allocation-free call, for the FP16 and the FP8 engine."""
+    from chessrl_b200 import Engine, positions
+    import chessrl_b200 as crl
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=51)
+    n = 150
+    pos = positions.playout_positions(n, seed=3, max_plies=100)
+    planes = pos["planes112"]
+    packed = positions.pack_planes104(planes)
+    for dtype in (crl.DTYPE_F16, crl.DTYPE_F8E4M3):
+        eng = Engine(engine_cfg(cfg, dtype=dtype, chunk=64))
+        eng.load_state_dict(sd)
+        if dtype == crl.DTYPE_F8E4M3:
+            eng.calibrate(packed[:64].cuda(), layout="packed104")
+        kw = dict(legal_mask=pos["legal1858"].cuda(), policy_softmax=True)
+        a = eng.forward(planes.cuda(), **kw)
+        b = eng.forward(packed.cuda(), layout="packed104", **kw)
+        assert torch.equal(a["policy"], b["policy"]) and torch.equal(a["wdl"], b["wdl"])
+        c = eng.forward(packed.pin_memory(), layout="packed104", host=True, legal_mask=pos["legal1858"], policy_softmax=True)
+        assert torch.equal(a["policy"].cpu(), c["policy"]) and torch.equal(a["wdl"].cpu(), c["wdl"])
+        rc, st = eng.last_status()
+        assert rc == 0 and st == 0
+    with pytest.raises(ValueError):
+        eng.forward(packed[:, :839].contiguous().cuda(), layout="packed104")
+    eng19 = Engine(engine_cfg(bt4spec.SpecConfig.reference_value(1, 64, 96, 2)))
+    eng19.load_state_dict(bt4spec.seeded_state_dict(bt4spec.BT4Spec(bt4spec.SpecConfig.reference_value(1, 64, 96, 2)), seed=1))
+    with pytest.raises(crl.CrlError):
+        eng19.forward(packed.cuda(), layout="packed104")
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""
