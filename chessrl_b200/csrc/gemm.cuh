@@ -40,6 +40,22 @@ struct GemmParams {
 };
 
 constexpr int kGemmThreads = 576;   // TMA warp + MMA warp + 16 epilogue warps
+
+// Optional cycle probes of the epilogue (compile with -DCRL_EPI_PROBE; the status buffer must then hold 64
+// ints): lane 0 of every epilogue warp adds its clock64 deltas per phase to status[8..19].
+#ifdef CRL_EPI_PROBE
+#define EPI_PROBE_DECL long long pr_t = 0, pr_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define EPI_PROBE_START() pr_t = clock64()
+#define EPI_PROBE(i) do { const long long n_ = clock64(); pr_acc[i] += n_ - pr_t; pr_t = n_; } while (0)
+#define EPI_PROBE_COUNT(i) pr_acc[i] += 1
+#define EPI_PROBE_FLUSH() do { if (lane == 0) for (int i_ = 0; i_ < 12; ++i_) atomicAdd(p.status + 8 + i_, static_cast<int>(pr_acc[i_] >> (i_ == 0 || i_ == 8 ? 0 : 4))); } while (0)
+#else
+#define EPI_PROBE_DECL
+#define EPI_PROBE_START()
+#define EPI_PROBE(i)
+#define EPI_PROBE_COUNT(i)
+#define EPI_PROBE_FLUSH()
+#endif
 constexpr int kEpiWarps = 16;
 
 // PAIR = 1: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs. Each CTA stages
@@ -187,11 +203,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = (t / tiles_n) * TM + rank * BM;                  // this CTA's rows of A
         const int n0 = (t % tiles_n) * BN + rank * (PAIR ? BN / 2 : 0);  // this CTA's rows of W
         for (int kb = 0; kb < kblocks; ++kb) {
+#ifdef CRL_EPI_PROBE
+          const long long pw0 = clock64();
+#endif
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
             atomicCAS(p.status, 0, kDevTimeoutProducer);
             ok = false;
             break;
           }
+#ifdef CRL_EPI_PROBE
+          atomicAdd(p.status + 26 + rank, static_cast<int>((clock64() - pw0) >> 4));
+#endif
           const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           if constexpr (PAIR) {
@@ -219,13 +241,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0;
       int local = 0;
       bool ok = true;
+#ifdef CRL_EPI_PROBE
+      long long mt = clock64(), m_acc[4] = {0, 0, 0, 0};
+#define MMA_PROBE(i) do { const long long n_ = clock64(); m_acc[i] += n_ - mt; mt = n_; } while (0)
+#else
+#define MMA_PROBE(i)
+#endif
       for (int t = worker; t < num_tiles && ok; t += num_workers, ++local) {
         const int as = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
+        MMA_PROBE(3);
         if (!mbar_wait(tempty_bar(as), aph ^ 1u)) {
           atomicCAS(p.status, 0, kDevTimeoutMma);
           break;
         }
+        MMA_PROBE(0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -234,6 +264,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ok = false;
             break;
           }
+          MMA_PROBE(1);
           tc_fence_after();
           const uint32_t a_src = base + s * Cfg::STAGE_BYTES;
           const uint64_t da = umma_desc_k_sw128(a_src);
@@ -245,9 +276,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           tc_commit<PAIR>(empty_bar(s));    // frees the stage (in both CTAs) once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1u; }
+          MMA_PROBE(2);
         }
         if (ok) tc_commit<PAIR>(tfull_bar(as));   // accumulator complete
       }
+#ifdef CRL_EPI_PROBE
+      for (int i = 0; i < 4; ++i) atomicAdd(p.status + 20 + i, static_cast<int>(m_acc[i] >> 4));
+      atomicAdd(p.status + 24, local);
+#endif
     }
     __syncwarp();
   } else {
@@ -272,7 +308,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool staged_ok = p.use_tma_store != 0 && al_r && p.out_dtype != kOutF32;
     bool alive = true;
     int local = 0;
+    EPI_PROBE_DECL;
     for (int t = worker; t < num_tiles; t += num_workers, ++local) {
+      EPI_PROBE_START();
+      EPI_PROBE_COUNT(8);
       const int as = local & 1;
       const uint32_t aph = (local >> 1) & 1u;
       const int m0 = (t / tiles_n) * TM + rank * BM;   // first row of this CTA's accumulator half
@@ -285,12 +324,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int e = et; e < BN; e += kEpiWarps * 32) cs_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.col_scale + n0 + e) : 0.0f;
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
+      EPI_PROBE(9);
       if (alive && !mbar_wait(tfull_bar(as), aph)) {
         if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
         alive = false;           // keep iterating so that the named barrier above stays balanced
       }
       if (!alive) continue;
       tc_fence_after();
+      EPI_PROBE(7);
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const int rrow = p.res_mod > 0 ? row % p.res_mod : row;
@@ -319,6 +360,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t acc[32];
         tmem_ld_32x32(tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(as * BN + c * 32), acc);
         tmem_ld_wait();
+        EPI_PROBE_COUNT(0);
+        EPI_PROBE(1);
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -358,6 +401,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
           }
+          EPI_PROBE(2);
           if (p.residual != nullptr) {
             // transpose the coalesced residual rows through the staging tile into row-per-thread order
             if (lane == 0) bulk_wait_read0();   // the previous chunk's TMA store has read the tile
@@ -384,6 +428,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) bulk_wait_read0();
             __syncwarp();
           }
+          EPI_PROBE(3);
           // row-per-thread results -> swizzled staging tile (the layout a TMA box with the 64-byte,
           // for e4m3 32-byte, swizzle expects) -> one TMA store per warp and chunk; rows and columns
           // beyond the matrix are clipped by the TMA unit
@@ -408,12 +453,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
           }
+          EPI_PROBE(4);
           fence_proxy_async_smem();   // every writing lane, before the barrier (the documented order)
           __syncwarp();
+          EPI_PROBE(5);
           if (lane == 0) {
             tma_store_2d(&tmC, stage_u, c0, m0 + quarter * 32);
             bulk_commit();
           }
+          EPI_PROBE(6);
         } else if (c0 + 32 <= p.N && vec_ok) {
           // direct path (f32 output, per-column scales): each thread stores its own row segment
           if (p.col_scale != nullptr) {
@@ -484,7 +532,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (PAIR && rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
         else mbar_arrive(tempty_bar(as));
       }
+      EPI_PROBE(10);
     }
+    EPI_PROBE_FLUSH();
     if (lane == 0) bulk_wait_all();   // this warp's TMA stores have left shared memory and landed
     __syncwarp();
   }
