@@ -387,7 +387,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           // activation: the switch sits outside the element loop so that the 32 independent
           // evaluations interleave
-          if (p.act == kActMish) {
+          // Mish into an e4m3 output runs on packed f16 pairs at the conversion below
+          const bool mish8 = p.act == kActMish && p.out_dtype == kOutE4M3 && p.residual == nullptr;
+          if (mish8) {
+          } else if (p.act == kActMish) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = act_mish(v[j]);
           } else if (p.act == kActGelu) {
@@ -397,7 +400,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
           }
-          if (p.out_dtype == kOutE4M3) {
+          if (p.out_dtype == kOutE4M3 && !mish8) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
           }
@@ -438,6 +441,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t w0 = pack_f16x2(v[q * 8 + 0], v[q * 8 + 1]), w1 = pack_f16x2(v[q * 8 + 2], v[q * 8 + 3]);
               const uint32_t w2 = pack_f16x2(v[q * 8 + 4], v[q * 8 + 5]), w3 = pack_f16x2(v[q * 8 + 6], v[q * 8 + 7]);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_off(lane, q)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+          } else if (mish8) {
+            const __half2 s2 = __float2half2_rn(p.out_scale);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float* e = &v[q * 16 + j * 4];
+                const uint32_t y0 = mish_f16x2(pack_f16x2(e[0], e[1])), y1 = mish_f16x2(pack_f16x2(e[2], e[3]));
+                const __half2 z0 = __hmul2(*reinterpret_cast<const __half2*>(&y0), s2);
+                const __half2 z1 = __hmul2(*reinterpret_cast<const __half2*>(&y1), s2);
+                w[j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&z0), __NV_SATFINITE, __NV_E4M3)) |
+                       (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&z1), __NV_SATFINITE, __NV_E4M3)) << 16);
+              }
+              const uint32_t off8 = stage_u + lane * 32 + ((q ^ ((lane >> 2) & 1)) << 4);   // 32-byte swizzle
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
             }
           } else {
 #pragma unroll
