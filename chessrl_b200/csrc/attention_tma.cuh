@@ -214,4 +214,212 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
   __syncwarp();
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention with Q, K and V arriving as e4m3 (the FP8 engine's QKV projection writes them that way,
+// one per-tensor scale s: byte value = real value * s). A (board, head) item is then three 64 x 32-byte tiles
+// plus the 4 KB e4m3 bias tile - 10 KB per warp instead of 16 - and half the HBM bytes of the f16 form.
+// The bytes become f16 in registers right after ldmatrix:
+//   Q, K : a non-transposed 8x8 "b16" matrix holds 16 e4m3 per row, four consecutive k per thread; the two
+//          converted pairs serve as the k and k+8 halves of the m16n8k16 fragment. Q and K use the same
+//          (permuted) k order, which a dot product does not see. Q is multiplied by 1/s^2 on the way so that
+//          the f16 score accumulation sees real-valued scores.
+//   V    : the transposed load hands a thread (V[j][2g], V[j][2g+1], V[j+1][2g], V[j+1][2g+1]); one byte
+//          permute regroups them into the token pairs of columns 2g and 2g+1, i.e. the B fragments of two MMAs
+//          whose outputs interleave to four consecutive head-dim bytes per thread.
+// Output: e4m3 context (x out_mult = out_scale / s), written through the Q tile and a TMA store as above.
+// ---------------------------------------------------------------------------------------------
+struct AttnTma8Params {
+  int B, H;
+  float scale;           // softmax scale
+  float q_mult;          // 1 / s^2
+  int has_bias;          // 0 none, 2 e4m3 tile
+  float bias_mult;       // bias value = byte * bias_mult
+  float out_mult;        // context byte = context * out_mult
+  int d;
+  int* status;
+};
+
+template <int NW>
+struct AttnTma8Smem {
+  static constexpr int PER_WARP = 10 * 1024;   // Q/out 2K | K 2K | V 2K | bias 4K
+  static constexpr int BAR_OFF = NW * PER_WARP;
+  static constexpr int BYTES = BAR_OFF + NW * 8 + 1024;
+};
+
+__device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// 16-byte piece c (0/1) of row r in a 64 x 32-byte tile written with the 32-byte swizzle
+__device__ __forceinline__ uint32_t tile8_off(int r, int c) { return r * 32 + ((c ^ ((r >> 2) & 1)) << 4); }
+
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+attention_tma8_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmBias,
+                      const __grid_constant__ CUtensorMap tmOut, const AttnTma8Params p) {
+  using SM = AttnTma8Smem<NW>;
+  extern __shared__ uint8_t smem_at_raw[];
+  const uint32_t raw = smem_u32(smem_at_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t wbase = base + warp * SM::PER_WARP;
+  const uint32_t bar = base + SM::BAR_OFF + warp * 8;
+  const uint8_t* sB = smem_at_raw + (base - raw) + warp * SM::PER_WARP + 6144;
+  const uint32_t sQ = wbase, sK = wbase + 2048, sV = wbase + 4096;
+  const uint32_t out_u = wbase;          // the context tile overlays the Q tile
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (warp == 0) { tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmBias); tma_prefetch_desc(&tmOut); }
+  }
+  __syncwarp();
+
+  const long long items = (long long)p.B * p.H;
+  const long long first = (long long)blockIdx.x * NW + warp;
+  const long long stride = (long long)gridDim.x * NW;
+  const uint32_t stage_bytes = 3u * 2048u + (p.has_bias ? 4096u : 0u);
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t k_scale = pack_h2(p.scale * 1.4426950408889634f, p.scale * 1.4426950408889634f);
+  const uint32_t k_bias = pack_h2(p.bias_mult * 1.4426950408889634f, p.bias_mult * 1.4426950408889634f);
+  const uint32_t q_mul = pack_h2(p.q_mult, p.q_mult);
+  int it = 0;
+  for (long long item = first; item < items; item += stride, ++it) {
+    const int board = static_cast<int>(item / p.H), h = static_cast<int>(item % p.H);
+    if (lane == 0) {
+      bulk_wait_read0();                 // the previous context tile has been read out of the Q region
+      mbar_expect_tx(bar, stage_bytes);
+      tma_load_2d(sQ, &tmQKV, h * 32, board * 64, bar);
+      tma_load_2d(sK, &tmQKV, p.d + h * 32, board * 64, bar);
+      tma_load_2d(sV, &tmQKV, 2 * p.d + h * 32, board * 64, bar);
+      if (p.has_bias) tma_load_2d(wbase + 6144, &tmBias, 0, static_cast<int>(item * 64), bar);
+    }
+    if (!mbar_wait(bar, it & 1)) {
+      if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue + 10);
+      break;
+    }
+
+    for (int half = 0; half < 2; ++half) {
+      uint32_t sh[2][8][2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int n = 0; n < 8; ++n) sh[u][n][0] = sh[u][n][1] = 0u;
+      // Q fragments of both 16-row slabs, both k steps: a[u][ks] = {rows g | g+8} x {first | second pair}
+      uint32_t a[2][2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        uint32_t r0, r1, r2, r3;   // (rows g, bytes 0..15), (rows g+8, 0..15), (rows g, 16..31), (rows g+8, 16..31)
+        ldsm_x4(sQ + tile8_off((half * 2 + u) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, lane >> 4), r0, r1, r2, r3);
+        a[u][0][0] = hmul2_u32(e4m3x2_to_h2(r0 & 0xffffu), q_mul); a[u][0][1] = hmul2_u32(e4m3x2_to_h2(r1 & 0xffffu), q_mul);
+        a[u][0][2] = hmul2_u32(e4m3x2_to_h2(r0 >> 16), q_mul);     a[u][0][3] = hmul2_u32(e4m3x2_to_h2(r1 >> 16), q_mul);
+        a[u][1][0] = hmul2_u32(e4m3x2_to_h2(r2 & 0xffffu), q_mul); a[u][1][1] = hmul2_u32(e4m3x2_to_h2(r3 & 0xffffu), q_mul);
+        a[u][1][2] = hmul2_u32(e4m3x2_to_h2(r2 >> 16), q_mul);     a[u][1][3] = hmul2_u32(e4m3x2_to_h2(r3 >> 16), q_mul);
+      }
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t r0, r1, r2, r3;   // (keys 16np+g, bytes 0..15), (same keys, 16..31), (keys +8, 0..15), (keys +8, 16..31)
+        ldsm_x4(sK + tile8_off(np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8, (lane >> 3) & 1), r0, r1, r2, r3);
+        const uint32_t b00 = e4m3x2_to_h2(r0 & 0xffffu), b01 = e4m3x2_to_h2(r0 >> 16);
+        const uint32_t b10 = e4m3x2_to_h2(r1 & 0xffffu), b11 = e4m3x2_to_h2(r1 >> 16);
+        const uint32_t c00 = e4m3x2_to_h2(r2 & 0xffffu), c01 = e4m3x2_to_h2(r2 >> 16);
+        const uint32_t c10 = e4m3x2_to_h2(r3 & 0xffffu), c11 = e4m3x2_to_h2(r3 >> 16);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          mma16816_h(sh[u][2 * np], a[u][0][0], a[u][0][1], a[u][0][2], a[u][0][3], b00, b01);
+          mma16816_h(sh[u][2 * np], a[u][1][0], a[u][1][1], a[u][1][2], a[u][1][3], b10, b11);
+          mma16816_h(sh[u][2 * np + 1], a[u][0][0], a[u][0][1], a[u][0][2], a[u][0][3], c00, c01);
+          mma16816_h(sh[u][2 * np + 1], a[u][1][0], a[u][1][1], a[u][1][2], a[u][1][3], c10, c11);
+        }
+      }
+      float inv[2][2];
+      float o[2][5][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int n = 0; n < 5; ++n) o[u][n][0] = o[u][n][1] = o[u][n][2] = o[u][n][3] = 0.0f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r0 = (half * 2 + u) * 16 + g;
+        if (p.has_bias) {
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+            const int ra = r0, rb = r0 + 8;
+            const uint16_t wa = *reinterpret_cast<const uint16_t*>(sB + ra * 64 + (((n >> 1) ^ ((ra >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
+            const uint16_t wb = *reinterpret_cast<const uint16_t*>(sB + rb * 64 + (((n >> 1) ^ ((rb >> 1) & 3)) << 4) + (n & 1) * 8 + 2 * t);
+            sh[u][n][0] = hfma2_u32(sh[u][n][0], k_scale, hmul2_u32(e4m3x2_to_h2(wa), k_bias));
+            sh[u][n][1] = hfma2_u32(sh[u][n][1], k_scale, hmul2_u32(e4m3x2_to_h2(wb), k_bias));
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+            sh[u][n][0] = hmul2_u32(sh[u][n][0], k_scale);
+            sh[u][n][1] = hmul2_u32(sh[u][n][1], k_scale);
+          }
+        }
+        uint32_t m0 = sh[u][0][0], m1 = sh[u][0][1];
+#pragma unroll
+        for (int n = 1; n < 8; ++n) { m0 = hmax2_u32(m0, sh[u][n][0]); m1 = hmax2_u32(m1, sh[u][n][1]); }
+        m0 = hmax2_u32(m0, __byte_perm(m0, m0, 0x1032));
+        m1 = hmax2_u32(m1, __byte_perm(m1, m1, 0x1032));
+        m0 = hmax2_u32(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+        m0 = hmax2_u32(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+        m1 = hmax2_u32(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+        m1 = hmax2_u32(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          sh[u][n][0] = hexp2_u32(hsub2_u32(sh[u][n][0], m0));
+          sh[u][n][1] = hexp2_u32(hsub2_u32(sh[u][n][1], m1));
+        }
+      }
+      // O = P V: o[u][2c] holds head-dim bytes 16c+4t and 16c+4t+2, o[u][2c+1] bytes 16c+4t+1 and 16c+4t+3;
+      // o[u][4] is the all-ones column (row sums)
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t r[4];   // (tokens 16kk+2t..,  bytes 0..15), (tokens 16kk+8+2t.., 0..15), (.., 16..31), (.., 16..31)
+        ldsm_x4_t(sV + tile8_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, lane >> 4), r[0], r[1], r[2], r[3]);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const uint32_t pa = __byte_perm(r[2 * c], 0u, 0x3120), pb = __byte_perm(r[2 * c + 1], 0u, 0x3120);
+          const uint32_t e0 = e4m3x2_to_h2(pa & 0xffffu), e1 = e4m3x2_to_h2(pb & 0xffffu);
+          const uint32_t o0 = e4m3x2_to_h2(pa >> 16), o1 = e4m3x2_to_h2(pb >> 16);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            mma16816(o[u][2 * c], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], e0, e1);
+            mma16816(o[u][2 * c + 1], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], o0, o1);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          mma16816(o[u][4], sh[u][2 * kk][0], sh[u][2 * kk][1], sh[u][2 * kk + 1][0], sh[u][2 * kk + 1][1], 0x3C003C00u, 0x3C003C00u);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) { inv[u][0] = p.out_mult / o[u][4][0]; inv[u][1] = p.out_mult / o[u][4][2]; }
+      __syncwarp();   // every lane has taken its Q fragments of these two slabs: their rows receive the context
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int ra = (half * 2 + u) * 16 + g, rb = ra + 8;
+        const float inv0 = inv[u][0], inv1 = inv[u][1];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const uint32_t a_lo = __nv_cvt_float2_to_fp8x2(make_float2(o[u][2 * c][0] * inv0, o[u][2 * c + 1][0] * inv0), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t a_hi = __nv_cvt_float2_to_fp8x2(make_float2(o[u][2 * c][1] * inv0, o[u][2 * c + 1][1] * inv0), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t b_lo = __nv_cvt_float2_to_fp8x2(make_float2(o[u][2 * c][2] * inv1, o[u][2 * c + 1][2] * inv1), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t b_hi = __nv_cvt_float2_to_fp8x2(make_float2(o[u][2 * c][3] * inv1, o[u][2 * c + 1][3] * inv1), __NV_SATFINITE, __NV_E4M3);
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(out_u + tile8_off(ra, c) + 4 * t), "r"(a_lo | (a_hi << 16)) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(out_u + tile8_off(rb, c) + 4 * t), "r"(b_lo | (b_hi << 16)) : "memory");
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();     // context tile complete, and every lane is done with K, V and the bias tile
+    if (lane == 0) {
+      tma_store_2d(&tmOut, out_u, h * 32, board * 64);
+      bulk_commit();
+    }
+  }
+  if (lane == 0) bulk_wait_all();
+  __syncwarp();
+}
+
 }  // namespace crl

@@ -36,7 +36,7 @@ struct LayerW {
   // INT8: per-output-channel symmetric weights and their scales
   int8_t *wqkv_q = nullptr, *wo_q = nullptr, *wff1_q = nullptr, *wff2_q = nullptr;
   float *cs_qkv = nullptr, *cs_o = nullptr, *cs_ff1 = nullptr, *cs_ff2 = nullptr;
-  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1;
+  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1, sa_qkv = 1;
 };
 
 struct ValueW {
@@ -385,6 +385,34 @@ int attention_tma_launch(crl_handle* h, const AttnTmaParams& t, const __half* qk
   return t.has_bias == 1 ? attention_tma_launch_t<11>(h, t, tq, tb, to, s) : attention_tma_launch_t<14>(h, t, tq, tb, to, s);
 }
 
+template <int NW>
+int attention_tma8_launch_t(crl_handle* h, const AttnTma8Params& t, const CUtensorMap& tq, const CUtensorMap& tb,
+                            const CUtensorMap& to, cudaStream_t s) {
+  static bool attr_set[64] = {};
+  if (h->device >= 0 && h->device < 64 && !attr_set[h->device]) {
+    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma8_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTma8Smem<NW>::BYTES));
+    attr_set[h->device] = true;
+  }
+  const long long items = static_cast<long long>(t.B) * t.H;
+  const long long want = (items + NW - 1) / NW;
+  const unsigned grid = static_cast<unsigned>(want < h->num_sms ? want : h->num_sms);
+  attention_tma8_kernel<NW><<<grid, NW * 32, AttnTma8Smem<NW>::BYTES, s>>>(tq, tb, to, t);
+  CRL_CUDA(h, cudaGetLastError());
+  return CRL_OK;
+}
+
+// e4m3 Q/K/V rows [M, 3d], e4m3 bias tiles, e4m3 context
+int attention_tma8_launch(crl_handle* h, const AttnTma8Params& t, const uint8_t* qkv8, const void* bias, void* out, cudaStream_t s) {
+  const uint64_t M = static_cast<uint64_t>(t.B) * 64;
+  CUtensorMap tq, tb, to;
+  std::memset(&tb, 0, sizeof(tb));
+  int rc = make_tmap_2d(&tq, qkv8, 1, 3ull * t.d, M, 3ull * t.d, 64, 32);
+  if (rc == kOk && t.has_bias == 2) rc = make_tmap_2d(&tb, bias, 1, 64, static_cast<uint64_t>(t.B) * t.H * 64, 64, 64, 64);
+  if (rc == kOk) rc = make_tmap_2d(&to, out, 1, t.d, M, t.d, 64, 32);
+  if (rc != kOk) return fail(h, rc, "attention: tensor map encoding failed");
+  return attention_tma8_launch_t<16>(h, t, tq, tb, to, s);
+}
+
 int act_of(const crl_config& c) { return c.act == CRL_ACT_MISH ? kActMish : kActGelu; }
 
 int value_head(crl_handle* h, const ValueW& vw, const __half* x, __half* v1, __half* v2, int64_t bc, float* out,
@@ -412,6 +440,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   const long long M = bc * 64;
   const bool f8 = c.dtype == CRL_DTYPE_F8E4M3 && !calib;
   const bool i8 = c.dtype == CRL_DTYPE_I8;
+  // FP8 engine on the TMA attention path: the QKV projection writes e4m3 and attention reads it
+  const bool qkv8 = f8 && h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN);
   int8_t* const xq = reinterpret_cast<int8_t*>(w.x8);
   const int act = act_of(c);
 
@@ -467,10 +497,12 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     {
       Lin q; q.m = M; q.n = 3 * d; q.k = d; q.c = w.t1; q.ldc = 3 * d; q.bias = L.bqkv;
       if (f8) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); }
+      if (qkv8) { q.out = kOutE4M3; q.out_scale = L.sa_qkv; }   // Q, K, V cross HBM as e4m3 (one scale for the three)
       else if (i8) { q.kind = kKindI8; q.a = w.x8; q.w = L.wqkv_q; q.row_scale = w.xs; q.col_scale = L.cs_qkv; }
       else { q.a = attn_in; q.w = L.wqkv; }
       q.lda = d; q.ldw = d;
       if ((rc = linear(h, q, s)) != CRL_OK) return rc;
+      if (calib && (rc = tap_amax(h, w.t1, M, 3 * d, l * 8 + 5, s)) != CRL_OK) return rc;
     }
     if (c.bias_mode == CRL_BIAS_SMOLGEN) {
       const int cc = c.smolgen_compress, hid = c.smolgen_hidden, gen = c.smolgen_gen;
@@ -502,9 +534,17 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if (f8) { a.out = nullptr; a.out8 = w.t2_8; a.out8_scale = L.sa_ctx; }
       else { a.out = w.t2; a.out8 = nullptr; a.out8_scale = 1.0f; }
       ProfScope ps(h, s, kCatAttention, 4.0 * M * 64 * d,
-                   static_cast<double>(M) * d * 2 * 3 + static_cast<double>(M) * d * (f8 ? 1 : 2) +
+                   static_cast<double>(M) * d * (qkv8 ? 1 : 2) * 3 + static_cast<double>(M) * d * (f8 ? 1 : 2) +
                        (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * (f8 ? 4096 : 8192) : 0.0));
-      if (h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN)) {
+      if (qkv8) {
+        AttnTma8Params t{};
+        t.B = static_cast<int>(bc); t.H = H; t.scale = a.scale; t.d = d; t.status = h->status_dev;
+        t.q_mult = 1.0f / (L.sa_qkv * L.sa_qkv);
+        t.has_bias = c.bias_mode == CRL_BIAS_SMOLGEN ? 2 : 0;
+        t.bias_mult = 1.0f / L.sa_bias;
+        t.out_mult = L.sa_ctx / L.sa_qkv;
+        if ((rc = attention_tma8_launch(h, t, reinterpret_cast<const uint8_t*>(w.t1), w.sg_bias, w.t2_8, s)) != CRL_OK) return rc;
+      } else if (h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN)) {
         AttnTmaParams t{};
         t.B = static_cast<int>(bc); t.H = H; t.scale = a.scale; t.d = d; t.status = h->status_dev;
         t.has_bias = c.bias_mode == CRL_BIAS_SMOLGEN ? (f8 ? 2 : 1) : 0;
@@ -1048,6 +1088,7 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
     h->layers[l].sa_ffn = mult(amax[l * 8 + 2]);
     h->layers[l].sa_hid = mult(amax[l * 8 + 3]);
     h->layers[l].sa_bias = mult(amax[l * 8 + 4]);
+    h->layers[l].sa_qkv = mult(amax[l * 8 + 5]);
   }
   h->calibrated = true;
   return CRL_OK;
