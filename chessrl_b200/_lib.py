@@ -19,7 +19,7 @@ VALUE_NONE, VALUE_WDL, VALUE_WDL_Q = 0, 1, 2
 DTYPE_F16, DTYPE_F8E4M3, DTYPE_I8 = 0, 1, 2
 LAYOUT_NHWC_F32, LAYOUT_NHWC_F16, LAYOUT_NCHW_F16, LAYOUT_NCHW_F32, LAYOUT_PACKED104 = 0, 1, 2, 3, 4
 PACKED104_BYTES = 840
-MASK_NONE, MASK_BITS, MASK_ADDITIVE = 0, 1, 2
+MASK_NONE, MASK_BITS, MASK_ADDITIVE, MASK_FROM_RECORDS = 0, 1, 2, 3
 OUT_F32, OUT_F16 = 0, 1
 VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
 
@@ -28,7 +28,7 @@ EXPORTS = [
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
     "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static", "crl_perft", "crl_fen_to_planes19", "crl_legal_mask_1929",
-    "crl_playout_positions", "crl_pack_planes104",
+    "crl_playout_positions", "crl_pack_planes104", "crl_legal_masks_packed104",
 ]
 
 
@@ -50,6 +50,7 @@ class IO(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
         ("policy_vocab", ctypes.c_int32), ("black_rows", ctypes.c_void_p),
+        ("move_out", ctypes.c_void_p), ("move_uniform", ctypes.c_void_p), ("move_temperature", ctypes.c_float),
     ]
 
 
@@ -121,6 +122,8 @@ def load():
     lib.crl_playout_positions.restype = ctypes.c_int
     lib.crl_pack_planes104.argtypes = [vp, i32, i64, vp]
     lib.crl_pack_planes104.restype = ctypes.c_int
+    lib.crl_legal_masks_packed104.argtypes = [vp, vp, i64, vp, i64, vp]
+    lib.crl_legal_masks_packed104.restype = ctypes.c_int
     lib.crl_vocab_move.argtypes = [ctypes.c_int, ctypes.c_char_p]
     lib.crl_vocab_move.restype = ctypes.c_int
     lib.crl_vocab_mirror_index.argtypes = [ctypes.c_int]

@@ -17,6 +17,7 @@
 #include "policy.cuh"
 #include "rows.cuh"
 #include "vocab.h"
+#include "movegen.cuh"
 
 using namespace crl;
 
@@ -80,7 +81,9 @@ struct crl_handle {
   ValueW vh, vq;
 
   // crl_forward_host staging (device) and workspace, grown on demand
+  short* plain_idx = nullptr;         // [4096] from*64+to -> entry of the 1858 list, -1 where none (device)
   void* st_black = nullptr; size_t st_black_b = 0;
+  void* st_move = nullptr; size_t st_move_b = 0;     // [B] int32 moves, then [B] f32 uniforms
   void *st_planes = nullptr, *st_mask = nullptr, *st_policy = nullptr, *st_wdl = nullptr, *st_q = nullptr, *st_ws = nullptr;
   size_t st_planes_b = 0, st_mask_b = 0, st_policy_b = 0, st_wdl_b = 0, st_q_b = 0, st_ws_b = 0;
 };
@@ -218,6 +221,7 @@ struct Workspace {
   __half *flat;     // [bc, 4096] policy scores (dense form)
   float* logits;    // [bc, 1929] f32 (dense form)
   __half *v2, *v2q;
+  uint8_t* legal;      // [bc, 236] legal-move bitsets generated from the packed records
   size_t total;
 };
 
@@ -263,6 +267,7 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc) {
   w.logits = reinterpret_cast<float*>(take((dense || lm) ? static_cast<size_t>(bc) * 2048 * 4 : 0));
   w.v2 = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
+  w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(bc) * 236 : 0));
   w.total = off;
   return w;
 }
@@ -650,7 +655,17 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     const void* mask_row = nullptr;
     if (mask != nullptr && io->mask_mode == CRL_MASK_BITS) mask_row = mask + b0 * io->mask_stride;
     if (mask != nullptr && io->mask_mode == CRL_MASK_ADDITIVE) mask_row = mask + b0 * io->mask_stride * 4;
-    const int mask_mode = mask_row != nullptr ? io->mask_mode : CRL_MASK_NONE;
+    int mask_mode = mask_row != nullptr ? io->mask_mode : CRL_MASK_NONE;
+    long long mask_ld = io->mask_stride;
+    if (io->mask_mode == CRL_MASK_FROM_RECORDS) {
+      MoveGenParams mg{};
+      mg.recs = static_cast<const uint8_t*>(io->planes) + b0 * CRL_PACKED104_BYTES; mg.batch = bc;
+      mg.plain_idx = h->plain_idx; mg.bits = w.legal; mg.stride = 236;
+      legal_mask_packed104_kernel<<<static_cast<unsigned>((bc + 63) / 64), 64, 0, s>>>(mg);
+      CRL_CUDA(h, cudaGetLastError());
+      ++h->launches;
+      mask_row = w.legal; mask_mode = CRL_MASK_BITS; mask_ld = 236;
+    }
     float* out32 = io->policy_dtype == CRL_OUT_F32 ? static_cast<float*>(io->policy_out) + b0 * io->policy_stride : nullptr;
     __half* out16 = io->policy_dtype == CRL_OUT_F16 ? static_cast<__half*>(io->policy_out) + b0 * io->policy_stride : nullptr;
     PolicyParams p{};
@@ -659,7 +674,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       p.flat = w.flat;
     } else {
       p.gather_idx = h->gather_idx; p.gather_promo = h->gather_promo; p.n_moves = n_moves;
-      p.mask = mask_row; p.mask_mode = mask_mode; p.mask_ld = io->mask_stride; p.softmax = io->policy_softmax;
+      p.mask = mask_row; p.mask_mode = mask_mode; p.mask_ld = mask_ld; p.softmax = io->policy_softmax;
       p.out_f32 = out32; p.out_f16 = out16; p.out_ld = io->policy_stride;
       if (io->policy_vocab == CRL_VOCAB_RL1929) {
         p.mirror = h->mirror_idx; p.out_width = 1929;
@@ -675,7 +690,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       e.m = bc; e.n = 1929; e.k = 4096;
       if ((rc = linear(h, e, s)) != CRL_OK) return rc;
       MaskRowsParams m{};
-      m.logits = w.logits; m.ld = 2048; m.n = 1929; m.mask = mask_row; m.mask_mode = mask_mode; m.mask_ld = io->mask_stride;
+      m.logits = w.logits; m.ld = 2048; m.n = 1929; m.mask = mask_row; m.mask_mode = mask_mode; m.mask_ld = mask_ld;
       m.softmax = io->policy_softmax; m.out_f32 = out32; m.out_f16 = out16; m.out_ld = io->policy_stride;
       mask_rows_kernel<<<static_cast<unsigned>(bc), 128, 0, s>>>(m);
       CRL_CUDA(h, cudaGetLastError());
@@ -693,20 +708,28 @@ int check_io(crl_handle* h, const crl_io* io) {
   if (io->layout < 0 || io->layout > CRL_LAYOUT_PACKED104) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
   if (io->layout == CRL_LAYOUT_PACKED104 && h->cfg.planes != 112) return fail(h, CRL_ERR_INVALID, "the packed layout holds 112 planes");
   if (io->layout == CRL_LAYOUT_PACKED104 && (reinterpret_cast<uintptr_t>(io->planes) & 3) != 0) return fail(h, CRL_ERR_INVALID, "packed planes must be 4-byte aligned");
-  if (io->mask_mode < 0 || io->mask_mode > 2) return fail(h, CRL_ERR_INVALID, "unknown mask mode");
+  if (io->mask_mode < 0 || io->mask_mode > CRL_MASK_FROM_RECORDS) return fail(h, CRL_ERR_INVALID, "unknown mask mode");
+  if (io->mask_mode == CRL_MASK_FROM_RECORDS && (io->layout != CRL_LAYOUT_PACKED104 || h->cfg.policy_mode != CRL_POLICY_GATHER1858))
+    return fail(h, CRL_ERR_INVALID, "masks from records need the packed input layout and the 1858-move gather head");
   const int n_moves = crl_num_moves(h);
-  if (io->policy_out != nullptr) {
+  if (io->policy_out != nullptr || io->move_out != nullptr) {
     if (n_moves == 0) return fail(h, CRL_ERR_INVALID, "policy_out given but the configuration has no policy head");
     if (io->policy_vocab != CRL_VOCAB_NATIVE && io->policy_vocab != CRL_VOCAB_RL1929) return fail(h, CRL_ERR_INVALID, "unknown policy_vocab");
     if (io->policy_vocab == CRL_VOCAB_RL1929 && h->cfg.policy_mode != CRL_POLICY_GATHER1858)
       return fail(h, CRL_ERR_INVALID, "policy_vocab RL1929 needs the 1858-move gather head");
-    if (io->policy_stride < (io->policy_vocab == CRL_VOCAB_RL1929 ? 1929 : n_moves))
+    if (io->policy_out != nullptr && io->policy_stride < (io->policy_vocab == CRL_VOCAB_RL1929 ? 1929 : n_moves))
       return fail(h, CRL_ERR_SHAPE, "policy_stride smaller than the move count");
-    if (io->policy_dtype != CRL_OUT_F32 && io->policy_dtype != CRL_OUT_F16) return fail(h, CRL_ERR_INVALID, "unknown policy dtype");
+    if (io->policy_out != nullptr && io->policy_dtype != CRL_OUT_F32 && io->policy_dtype != CRL_OUT_F16)
+      return fail(h, CRL_ERR_INVALID, "unknown policy dtype");
     if (io->legal_mask != nullptr && io->mask_mode == CRL_MASK_BITS && io->mask_stride * 8 < n_moves)
       return fail(h, CRL_ERR_SHAPE, "mask_stride too small for a bitset over the moves");
     if (io->legal_mask != nullptr && io->mask_mode == CRL_MASK_ADDITIVE && io->mask_stride < n_moves)
       return fail(h, CRL_ERR_SHAPE, "mask_stride smaller than the move count");
+  }
+  if (io->move_out != nullptr) {
+    if (n_moves == 0) return fail(h, CRL_ERR_INVALID, "move_out given but the configuration has no policy head");
+    if (io->move_temperature < 0.0f || !(io->move_temperature == io->move_temperature))
+      return fail(h, CRL_ERR_INVALID, "move_temperature must be >= 0");
   }
   if (io->wdl_out != nullptr && h->cfg.value_mode == CRL_VALUE_NONE)
     return fail(h, CRL_ERR_INVALID, "wdl_out given but the configuration has no value head");
@@ -731,6 +754,21 @@ int run_batch(crl_handle* h, const crl_io* io, bool calib) {
     const int64_t bc = std::min<int64_t>(chunk, io->batch - b0);
     const int rc = forward_chunk(h, io, b0, bc, w, calib, s);
     if (rc != CRL_OK) return rc;
+  }
+  if (io->move_out != nullptr && !calib) {
+    SampleParams sp{};
+    sp.r32 = io->policy_dtype == CRL_OUT_F32 ? static_cast<const float*>(io->policy_out) : nullptr;
+    sp.r16 = io->policy_dtype == CRL_OUT_F16 ? static_cast<const __half*>(io->policy_out) : nullptr;
+    sp.ld = io->policy_stride;
+    sp.n = io->policy_vocab == CRL_VOCAB_RL1929 ? 1929 : crl_num_moves(h);
+    sp.rows = io->batch;
+    sp.is_prob = io->policy_softmax;
+    sp.inv_t = io->move_temperature > 0.0f ? 1.0f / io->move_temperature : 0.0f;
+    sp.u = io->move_uniform;
+    sp.out = io->move_out;
+    sample_rows_kernel<<<static_cast<unsigned>((io->batch + 7) / 8), 256, 0, s>>>(sp);
+    CRL_CUDA(h, cudaGetLastError());
+    ++h->launches;
   }
   return CRL_OK;
 }
@@ -826,7 +864,7 @@ void crl_destroy(crl_handle* h) {
   cudaSetDevice(h->device);
   for (void* p : h->allocs) cudaFree(p);
   for (auto& r : h->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
-  for (void* p : {h->st_black, h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
+  for (void* p : {h->st_move, h->st_black, h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
     if (p != nullptr) cudaFree(p);
   delete h;
 }
@@ -1026,6 +1064,14 @@ int crl_finalize(crl_handle* h) {
     if ((rc = upload_f32(h, &h->b_qk, bqk.data(), rows)) != CRL_OK) return rc;
   }
   if (c.policy_mode == CRL_POLICY_DENSE4096) UP16(h->w_ph, "policy_head.weight", 1929, 4096, 4096);
+  {
+    const Vocab& v = Vocab::get();
+    std::vector<short> plain(4096, -1);
+    for (size_t i = 0; i < v.from_to.size(); ++i)
+      if (v.promo[i] == 0) plain[v.from_to[i]] = static_cast<short>(i);
+    if ((rc = dev_alloc(h, &h->plain_idx, plain.size())) != CRL_OK) return rc;
+    CRL_CUDA(h, cudaMemcpy(h->plain_idx, plain.data(), plain.size() * sizeof(short), cudaMemcpyHostToDevice));
+  }
   if (c.policy_mode == CRL_POLICY_GATHER1858) {
     const Vocab& v = Vocab::get();
     if ((rc = dev_alloc(h, &h->gather_idx, v.from_to.size())) != CRL_OK) return rc;
@@ -1060,6 +1106,7 @@ size_t crl_workspace_bytes(const crl_handle* h, int64_t batch) {
 int crl_forward(crl_handle* h, const crl_io* io) {
   int rc = check_io(h, io);
   if (rc != CRL_OK) return rc;
+  if (io->move_out != nullptr && io->policy_out == nullptr) return fail(h, CRL_ERR_INVALID, "move_out needs policy_out (the rows it reads)");
   h->launches = 0;
   return run_batch(h, io, false);
 }
@@ -1094,6 +1141,19 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
   return CRL_OK;
 }
 
+int crl_legal_masks_packed104(crl_handle* h, const void* packed, int64_t count, uint8_t* bits, int64_t stride, void* stream) {
+  if (h == nullptr) return CRL_ERR_INVALID;
+  if (!h->finalized) return fail(h, CRL_ERR_NOT_FINALIZED, "crl_finalize has not run");
+  if (count < 0 || stride < 233 || (count > 0 && (packed == nullptr || bits == nullptr))) return fail(h, CRL_ERR_INVALID, "bad arguments");
+  if (count == 0) return CRL_OK;
+  CRL_CUDA(h, cudaSetDevice(h->device));
+  MoveGenParams mg{};
+  mg.recs = static_cast<const uint8_t*>(packed); mg.batch = count; mg.plain_idx = h->plain_idx; mg.bits = bits; mg.stride = stride;
+  legal_mask_packed104_kernel<<<static_cast<unsigned>((count + 63) / 64), 64, 0, static_cast<cudaStream_t>(stream)>>>(mg);
+  CRL_CUDA(h, cudaGetLastError());
+  return CRL_OK;
+}
+
 int crl_forward_host(crl_handle* h, const crl_io* io) {
   int rc = check_io(h, io);
   if (rc != CRL_OK) return rc;
@@ -1105,7 +1165,10 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
   const size_t pb = plane_bytes(h, io->layout) * B;
   const size_t esz = io->policy_dtype == CRL_OUT_F32 ? 4 : 2;
   const size_t mb = io->legal_mask == nullptr ? 0 : (io->mask_mode == CRL_MASK_BITS ? B * io->mask_stride : (io->mask_mode == CRL_MASK_ADDITIVE ? B * io->mask_stride * 4 : 0));
-  const size_t ob = io->policy_out != nullptr ? B * io->policy_stride * esz : 0;
+  // moves without policy rows: the rows live in the staging buffer only (f16, dense) and are not copied back
+  const bool own_rows = io->policy_out == nullptr && io->move_out != nullptr;
+  const size_t own_stride = io->policy_vocab == CRL_VOCAB_RL1929 ? 1929 : static_cast<size_t>(crl_num_moves(h));
+  const size_t ob = io->policy_out != nullptr ? B * io->policy_stride * esz : (own_rows ? B * own_stride * 2 : 0);
   if ((rc = grow(h, &h->st_planes, &h->st_planes_b, pb)) != CRL_OK) return rc;
   if (mb > 0 && (rc = grow(h, &h->st_mask, &h->st_mask_b, mb)) != CRL_OK) return rc;
   if (ob > 0 && (rc = grow(h, &h->st_policy, &h->st_policy_b, ob)) != CRL_OK) return rc;
@@ -1118,7 +1181,16 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
     if ((rc = grow(h, &h->st_black, &h->st_black_b, B)) != CRL_OK) return rc;
     CRL_CUDA(h, cudaMemcpyAsync(h->st_black, io->black_rows, B, cudaMemcpyHostToDevice, s));
   }
+  if (io->move_out != nullptr) {
+    if ((rc = grow(h, &h->st_move, &h->st_move_b, B * 8)) != CRL_OK) return rc;
+    if (io->move_uniform != nullptr)
+      CRL_CUDA(h, cudaMemcpyAsync(static_cast<char*>(h->st_move) + B * 4, io->move_uniform, B * 4, cudaMemcpyHostToDevice, s));
+  }
   crl_io dev = *io;
+  if (own_rows) { dev.policy_stride = static_cast<int64_t>(own_stride); dev.policy_dtype = CRL_OUT_F16; }
+  dev.move_out = io->move_out != nullptr ? static_cast<int32_t*>(h->st_move) : nullptr;
+  dev.move_uniform = (io->move_out != nullptr && io->move_uniform != nullptr)
+                         ? reinterpret_cast<const float*>(static_cast<char*>(h->st_move) + B * 4) : nullptr;
   dev.black_rows = (io->black_rows != nullptr && io->policy_vocab == CRL_VOCAB_RL1929) ? static_cast<const uint8_t*>(h->st_black) : nullptr;
   dev.planes = h->st_planes;
   dev.legal_mask = mb > 0 ? h->st_mask : nullptr;
@@ -1128,7 +1200,8 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
   dev.workspace = h->st_ws;
   dev.workspace_bytes = h->st_ws_b;
   if ((rc = run_batch(h, &dev, false)) != CRL_OK) return rc;
-  if (ob > 0) CRL_CUDA(h, cudaMemcpyAsync(io->policy_out, h->st_policy, ob, cudaMemcpyDeviceToHost, s));
+  if (ob > 0 && !own_rows) CRL_CUDA(h, cudaMemcpyAsync(io->policy_out, h->st_policy, ob, cudaMemcpyDeviceToHost, s));
+  if (io->move_out != nullptr) CRL_CUDA(h, cudaMemcpyAsync(io->move_out, h->st_move, B * 4, cudaMemcpyDeviceToHost, s));
   if (io->wdl_out != nullptr) CRL_CUDA(h, cudaMemcpyAsync(io->wdl_out, h->st_wdl, B * 12, cudaMemcpyDeviceToHost, s));
   if (io->q_out != nullptr) CRL_CUDA(h, cudaMemcpyAsync(io->q_out, h->st_q, B * 4, cudaMemcpyDeviceToHost, s));
   CRL_CUDA(h, cudaStreamSynchronize(s));
@@ -1146,6 +1219,7 @@ int crl_forward_static(crl_handle* h, const crl_io* io) {
   int rc = check_io(h, io);
   if (rc != CRL_OK) return rc;
   if (h->device < 0 || h->device >= 64) return fail(h, CRL_ERR_UNSUPPORTED, "device index beyond the static scratch table");
+  if (io->move_out != nullptr && io->policy_out == nullptr) return fail(h, CRL_ERR_INVALID, "move_out needs policy_out (the rows it reads)");
   const size_t need = crl_workspace_bytes(h, io->batch);
   if (need > static_cast<size_t>(CRL_STATIC_SCRATCH_BYTES))
     return fail(h, CRL_ERR_WORKSPACE, "batch " + std::to_string(io->batch) + " needs " + std::to_string(need) +

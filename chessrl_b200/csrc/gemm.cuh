@@ -11,7 +11,9 @@
 //   warps 2..17 : epilogue      - tcgen05.ld of the accumulator (a warp may read the 32 TMEM lanes
 //                 its rank modulo 4 selects; four warps share a lane quarter and split the columns;
 //                 the epilogue is latency-bound, so it wants many warps in flight),
-//                 then scale / bias / activation / residual, convert, store
+//                 then scale / bias / activation / residual, convert, store through a swizzled staging tile
+//                 and one TMA store per 32 x 32 chunk; in the RES variant the residual chunk arrives by TMA,
+//                 requested a chunk ahead
 // All waits are bounded (see ptx.cuh); a wait that runs out records a status code and unwinds.
 #pragma once
 #include <cuda_runtime.h>
@@ -37,6 +39,7 @@ struct GemmParams {
   float out_scale;         // multiplies the result before an e4m3 store
   int* status;             // device status word
   int use_tma_store;       // host built a tensor map for C (f16 / e4m3 output, 16-byte aligned pitch)
+  int use_tma_res;         // host built a tensor map for the residual (res_mod == 0, 16-byte aligned pitch)
 };
 
 constexpr int kGemmThreads = 576;   // TMA warp + MMA warp + 16 epilogue warps
@@ -62,7 +65,9 @@ constexpr int kEpiWarps = 16;
 // its own 128 rows of A and its own BN/2 rows of W, so a pair moves a third less data from L2 into
 // shared memory per FLOP than two independent CTAs; the leader CTA (cluster rank 0) issues the MMAs
 // for both, each CTA drains the 128 accumulator rows that land in its own tensor memory.
-template <int BN, int KIND, int PAIR = 0>
+// RES = 1 (pairs only): residual rows arrive by TMA into a per-warp tile; that variant trades one ring stage for
+// the tiles, the others keep five stages and carry none of its code.
+template <int BN, int KIND, int PAIR = 0, int RES = 0>
 struct GemmCfg {
   static constexpr int BM = 128;           // rows per CTA
   static constexpr int TM = PAIR ? 256 : 128;  // rows per tile
@@ -72,14 +77,16 @@ struct GemmCfg {
   static constexpr uint32_t A_BYTES = BM * 128;
   static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = PAIR ? 5 : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
+  static constexpr int STAGES = PAIR ? (RES ? 4 : 5) : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
   // after the stages: the bias and column-scale tables [2][2][BN] f32, one 32-row x 64-byte staging tile per epilogue
-  // warp (512-byte aligned: the TMA store swizzles by absolute address bits), then 128 bytes of
-  // mbarriers + TMEM slot
+  // warp (512-byte aligned: the TMA store swizzles by absolute address bits), one tile of the same shape per
+  // warp for residual rows arriving by TMA, then the mbarriers (ring, accumulators, one per epilogue warp for
+  // its residual tile) + TMEM slot
   static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
-  static constexpr uint32_t BAR_OFF = EPI_OFF + 4 * BN * 4 + kEpiWarps * 2048;
-  static constexpr uint32_t USED_BYTES = BAR_OFF + 128;
+  static constexpr uint32_t RES_OFF = EPI_OFF + 4 * BN * 4 + kEpiWarps * 2048;
+  static constexpr uint32_t BAR_OFF = RES_OFF + (RES ? kEpiWarps * 2048 : 0);
+  static constexpr uint32_t USED_BYTES = BAR_OFF + 128 + kEpiWarps * 8;
   static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + 896 /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
 };
@@ -135,11 +142,11 @@ __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off,
       static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-template <int BN, int KIND, int PAIR>
+template <int BN, int KIND, int PAIR, int RES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  using Cfg = GemmCfg<BN, KIND, PAIR>;
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES>;
   constexpr int BM = Cfg::BM, TM = Cfg::TM, BK = Cfg::BK, STAGES = Cfg::STAGES;
   // cluster rank (0 = leader) and the persistent worker this CTA belongs to
   const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
@@ -177,6 +184,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar0 + 128u + 8u * w, 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
@@ -306,6 +314,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool vec_ok = al_c && al_r && al_b && al_cs;
     // staged path: f16 / e4m3 outputs on aligned buffers (the shapes of the network's hot GEMMs)
     const bool staged_ok = p.use_tma_store != 0 && al_r && p.out_dtype != kOutF32;
+    // Residual rows by TMA: a warp's 32 x 32 f16 tile of the residual lands in its own shared-memory tile (the
+    // store box's shape and swizzle), requested one chunk ahead - the next chunk's as soon as this one's has been
+    // read, the next tile's first chunk before the wait for that tile's accumulator - so the HBM latency of the
+    // residual never sits between the accumulator and the store.
+    const bool tma_res = RES != 0 && p.use_tma_res != 0 && staged_ok && p.residual != nullptr && p.res_mod == 0 && p.N % 32 == 0;
+    const uint32_t res_u = base + Cfg::RES_OFF + ew * 2048;
+    const uint32_t rbar = bar0 + 128u + 8u * ew;
+    uint32_t rph = 0;
+    bool res_pending = false;
+    auto res_issue = [&](int tile, int c) {
+      if (lane == 0) {
+        mbar_expect_tx(rbar, 2048u);
+        tma_load_2d(res_u, &tmR, (tile % tiles_n) * BN + c * 32, (tile / tiles_n) * TM + rank * BM + quarter * 32, rbar);
+      }
+      res_pending = true;
+    };
+    if (RES != 0 && tma_res && part < BN / 32 && worker < num_tiles && (worker % tiles_n) * BN + part * 32 < p.N) res_issue(worker, part);
     bool alive = true;
     int local = 0;
     EPI_PROBE_DECL;
@@ -345,7 +370,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // residual rows in the coalesced mapping (lane -> row (lane>>2)+8i, 16-byte chunk lane&3),
         // requested before the accumulator is touched so that the latency overlaps
         uint4 rres[4];
-        if (staged && p.residual != nullptr) {
+        if (staged && p.residual != nullptr && !tma_res) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int gr = m0 + quarter * 32 + (lane >> 2) + 8 * i;
@@ -405,7 +430,37 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int j = 0; j < 32; ++j) v[j] *= p.out_scale;
           }
           EPI_PROBE(2);
-          if (p.residual != nullptr) {
+          if (RES != 0 && tma_res) {
+            if (!mbar_wait(rbar, rph)) {
+              if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
+              alive = false;
+              break;
+            }
+            rph ^= 1u;
+            res_pending = false;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                           : "r"(res_u + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)));
+              const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                v[q * 8 + 2 * j] += f.x;
+                v[q * 8 + 2 * j + 1] += f.y;
+              }
+            }
+            __syncwarp();   // every lane has read its row: the tile may be refilled
+            {
+              // this warp's next chunk: further along this tile, else the first chunk of its next tile
+              int nt = t, nc = c + 4;
+              if (nc >= BN / 32 || n0 + nc * 32 >= p.N) { nt = t + num_workers; nc = part; }
+              if (nt < num_tiles && nc < BN / 32 && (nt % tiles_n) * BN + nc * 32 < p.N) res_issue(nt, nc);
+            }
+            if (lane == 0) bulk_wait_read0();   // the previous chunk's TMA store has read the staging tile
+            __syncwarp();
+          } else if (p.residual != nullptr) {
             // transpose the coalesced residual rows through the staging tile into row-per-thread order
             if (lane == 0) bulk_wait_read0();   // the previous chunk's TMA store has read the tile
             __syncwarp();
@@ -555,6 +610,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       EPI_PROBE(10);
     }
     EPI_PROBE_FLUSH();
+    if (RES != 0 && res_pending) mbar_wait(rbar, rph);   // only after a timeout: no copy into this CTA's memory stays in flight
     if (lane == 0) bulk_wait_all();   // this warp's TMA stores have left shared memory and landed
     __syncwarp();
   }

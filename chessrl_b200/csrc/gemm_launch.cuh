@@ -65,14 +65,14 @@ struct GemmArgs {
   GemmParams p{};
 };
 
-template <int BN, int KIND, int PAIR = 0>
+template <int BN, int KIND, int PAIR = 0, int RES = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, KIND, PAIR>;
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -92,6 +92,13 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, 32 * oesz) == kOk)
       prm.use_tma_store = getenv("CRL_NO_TMA_STORE") ? 0 : 1;
   }
+  // residual rows arrive through the same box shape when the buffer allows a tensor map
+  CUtensorMap tmR;
+  std::memset(&tmR, 0, sizeof(tmR));
+  prm.use_tma_res = 0;
+  if (RES != 0 && prm.residual != nullptr && prm.res_mod == 0 && prm.use_tma_store &&
+      make_tmap_2d(&tmR, prm.residual, 2, prm.N, prm.M, static_cast<uint64_t>(prm.ldr) * 2, 32, 64) == kOk)
+    prm.use_tma_res = 1;
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
   if constexpr (PAIR) {
     // one 2-CTA cluster per pair of SMs
@@ -106,10 +113,10 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR>, tmA, tmB, tmC, prm) == cudaSuccess ? kOk : kErrCuda;
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
   } else {
     const int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tn_kernel<BN, KIND, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, prm);
+    gemm_tn_kernel<BN, KIND, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
     return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
   }
 }
@@ -123,8 +130,13 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
   // large problems: CTA pairs on 256 x 256 tiles (CRL_GEMM_PAIR=0 turns them off for comparisons)
   static const bool pair_ok = [] { const char* e = getenv("CRL_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
-  if (pair_ok && a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2)
-    return gemm_launch_t<256, KIND, 1>(a, num_sms, stream);
+  if (pair_ok && a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2) {
+    // a residual that a tensor map can describe goes through the variant that fetches it by TMA (measured on the
+    // out-projection, K = 1024: -18 %; with K = 1536 the ring stage it gives up costs more than the fetch saves)
+    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.out_dtype != kOutF32 && a.p.N % 32 == 0 && a.p.K <= 1024 &&
+                         a.p.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
+    return res_tma ? gemm_launch_t<256, KIND, 1, 1>(a, num_sms, stream) : gemm_launch_t<256, KIND, 1, 0>(a, num_sms, stream);
+  }
   if (bn == 64) return gemm_launch_t<64, KIND>(a, num_sms, stream);
   if (bn == 128) return gemm_launch_t<128, KIND>(a, num_sms, stream);
   return gemm_launch_t<256, KIND>(a, num_sms, stream);

@@ -235,4 +235,69 @@ __global__ void __launch_bounds__(128) mask_rows_kernel(const MaskRowsParams p) 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Move choice per policy row (model_bis.py:385-394), one warp per row: arg-max (lowest index on ties) or the
+// inverse-CDF draw for a caller-supplied uniform number: weights e_i = exp((x_i - max) / T) for logit rows,
+// (p_i / max p)^(1/T) for probability rows; the first index whose running sum exceeds u * total wins. Sums
+// run in double so that the order of additions does not move a boundary.
+// ---------------------------------------------------------------------------------------------
+struct SampleParams {
+  const float* r32; const __half* r16; long long ld;
+  int n; long long rows;
+  int is_prob; float inv_t;
+  const float* u;          // null: arg-max
+  int32_t* out;
+};
+
+__global__ void __launch_bounds__(256) sample_rows_kernel(const SampleParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + warp;
+  if (row >= p.rows) return;
+  auto val = [&](int i) -> float {
+    return p.r32 != nullptr ? p.r32[row * p.ld + i] : __half2float(p.r16[row * p.ld + i]);
+  };
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lane; i < p.n; i += 32) {
+    const float x = val(i);
+    if (x > best || bi == 0x7fffffff) { best = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+  }
+  if (p.u == nullptr || p.inv_t == 0.0f) {
+    if (lane == 0) p.out[row] = bi;
+    return;
+  }
+  auto weight = [&](int i) -> float {
+    const float x = val(i);
+    if (p.is_prob) return x > 0.0f ? powf(x / best, p.inv_t) : 0.0f;
+    return expf((x - best) * p.inv_t);
+  };
+  double part = 0.0;
+  for (int i = lane; i < p.n; i += 32) part += static_cast<double>(weight(i));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  const double thr = static_cast<double>(p.u[row]) * part;
+  double running = 0.0;
+  int pick = -1;
+  for (int base = 0; base < p.n && pick < 0; base += 32) {
+    const int i = base + lane;
+    double c = i < p.n ? static_cast<double>(weight(i)) : 0.0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double up = __shfl_up_sync(0xffffffffu, c, o);
+      if (lane >= o) c += up;
+    }
+    c += running;
+    const unsigned hit = __ballot_sync(0xffffffffu, i < p.n && c > thr);
+    if (hit != 0u) pick = base + (__ffs(hit) - 1);
+    running = __shfl_sync(0xffffffffu, c, 31);
+  }
+  if (lane == 0) p.out[row] = pick >= 0 ? pick : bi;   // u * total rounded up to the total itself: the mode
+}
+
 }  // namespace crl

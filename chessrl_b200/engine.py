@@ -151,14 +151,19 @@ class Engine:
     # ---- forward ---------------------------------------------------------------------------------
     def forward(self, planes, layout="nhwc", legal_mask=None, mask_mode=None, policy=True, wdl=True, q=False,
                 policy_softmax=False, wdl_softmax=True, policy_dtype=torch.float32, host=False, rl_vocab=False,
-                black_rows=None):
+                black_rows=None, moves=False, temperature=0.0, uniforms=None):
         """planes: [..., 8, 8, P] ("nhwc"), [B, P, 8, 8] ("nchw") or [B, 840] uint8 bit-packed records
         ("packed104", see positions.pack_planes104), on the engine's GPU (or on the host
         with host=True, which times like a user call: copies in, run, copies out, synchronise).
-        legal_mask: uint8 bitset [B, ceil(V/8)] (bit m of row b: move m legal) or float32 additive [B, V].
+        legal_mask: uint8 bitset [B, ceil(V/8)] (bit m of row b: move m legal), float32 additive [B, V], or the
+        string "records" (packed104 input, gather head): the legal moves are generated on the GPU.
         rl_vocab=True (gather head): rows of 1929 in the reference's own vocabulary, Black rows (uint8 flags in
         `black_rows`) rank-mirrored, like `map_leela_to_rl` after the server's softmax.
-        Returns a dict with `policy` [B, V], `wdl` [B, 3], `q` [B] as requested and available."""
+        moves=True: the move per position is chosen on the GPU (model_bis.py:385-394): arg-max for temperature 0
+        or without `uniforms`, else the inverse-CDF draw of softmax(logits / temperature) for the caller's
+        uniform numbers [B] in [0,1); `move` [B] int32 indexes the policy row. With policy=False only the
+        indices come back (4 bytes per position instead of the row).
+        Returns a dict with `policy` [B, V], `wdl` [B, 3], `q` [B], `move` [B] as requested and available."""
         planes = planes.contiguous()
         b = self._batch_of(planes, layout)
         dev = torch.device("cpu") if host else self.device
@@ -169,7 +174,11 @@ class Engine:
         io.layout = self._layout(planes, layout)
         io.batch = b
         out = {}
-        if legal_mask is not None:
+        if isinstance(legal_mask, str):
+            if legal_mask != "records":
+                raise ValueError('legal_mask is a tensor or the string "records"')
+            io.mask_mode = L.MASK_FROM_RECORDS      # legal moves generated on the GPU from the packed records
+        elif legal_mask is not None:
             legal_mask = legal_mask.contiguous()
             if mask_mode is None:
                 mask_mode = L.MASK_BITS if legal_mask.dtype == torch.uint8 else L.MASK_ADDITIVE
@@ -177,14 +186,27 @@ class Engine:
             io.mask_mode = mask_mode
             io.mask_stride = legal_mask.shape[-1]
         want_policy = policy and self.n_moves > 0
+        want_moves = moves and self.n_moves > 0
         kw = dict(device=dev, pin_memory=True) if host else dict(device=dev)
-        if want_policy:
+        if want_policy or want_moves:
             width = 1929 if rl_vocab else self.n_moves
-            out["policy"] = torch.empty(b, width, dtype=policy_dtype, **kw)
-            io.policy_out = out["policy"].data_ptr()
-            io.policy_dtype = L.OUT_F32 if policy_dtype == torch.float32 else L.OUT_F16
             io.policy_softmax = int(policy_softmax)
-            io.policy_stride = width
+            if want_policy or not host:      # the device entry point reads the moves from caller-owned rows
+                rows = torch.empty(b, width, dtype=policy_dtype, **kw)
+                io.policy_out = rows.data_ptr()
+                io.policy_dtype = L.OUT_F32 if policy_dtype == torch.float32 else L.OUT_F16
+                io.policy_stride = width
+                if want_policy:
+                    out["policy"] = rows
+            if want_moves:
+                out["move"] = torch.empty(b, dtype=torch.int32, **kw)
+                io.move_out = out["move"].data_ptr()
+                io.move_temperature = float(temperature)
+                if uniforms is not None:
+                    uniforms = uniforms.to(torch.float32).contiguous()
+                    if uniforms.device.type != dev.type or uniforms.numel() != b:
+                        raise ValueError(f"uniforms must be [B] on {dev}")
+                    io.move_uniform = uniforms.data_ptr()
             if rl_vocab:
                 io.policy_vocab = L.VOCAB_RL1929
                 if black_rows is not None:
@@ -205,6 +227,18 @@ class Engine:
             io.workspace = ws.data_ptr()
             io.workspace_bytes = ws.numel()
             self._check(self.lib.crl_forward(self._h, ctypes.byref(io)), "forward")
+        return out
+
+    def legal_masks(self, packed):
+        """[B, 840] uint8 packed records on the engine's GPU -> [B, 233] uint8 legal-move bitsets over the 1858-move
+        list in the mover's view, generated on the GPU (the rows `positions.playout_positions` calls legal1858)."""
+        packed = packed.contiguous()
+        if packed.dim() != 2 or packed.shape[1] != L.PACKED104_BYTES or packed.dtype != torch.uint8 or packed.device.type != "cuda":
+            raise ValueError("packed records are [B, 840] uint8 on the GPU")
+        out = torch.empty(packed.shape[0], 233, dtype=torch.uint8, device=packed.device)
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self.lib.crl_legal_masks_packed104(self._h, packed.data_ptr(), packed.shape[0], out.data_ptr(), 233, s),
+                    "legal_masks")
         return out
 
     def last_status(self):

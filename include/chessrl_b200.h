@@ -51,7 +51,10 @@ enum { CRL_LAYOUT_NHWC_F32 = 0, CRL_LAYOUT_NHWC_F16 = 1, CRL_LAYOUT_NCHW_F16 = 2
  *   byte 838, 839  ignored (plane 110 is empty, plane 111 is all ones).
  * The library expands it on the device into the token rows of the embedding GEMM. */
 #define CRL_PACKED104_BYTES 840
-enum { CRL_MASK_NONE = 0, CRL_MASK_BITS = 1, CRL_MASK_ADDITIVE = 2 };
+enum { CRL_MASK_NONE = 0, CRL_MASK_BITS = 1, CRL_MASK_ADDITIVE = 2, CRL_MASK_FROM_RECORDS = 3 };
+/* CRL_MASK_FROM_RECORDS (input layout CRL_LAYOUT_PACKED104, 1858-move gather head): the library generates the
+ * legal moves of every position on the device from its packed record and masks like CRL_MASK_BITS; legal_mask
+ * is ignored. Stands for the python-chess loop of model_bis.py:373-380 / pgn_to_input_data_decoder.py:35-42. */
 enum { CRL_OUT_F32 = 0, CRL_OUT_F16 = 1 };
 enum { CRL_VOCAB_NATIVE = 0, CRL_VOCAB_RL1929 = 1 };
 
@@ -110,6 +113,14 @@ typedef struct crl_io {
                               (Leela/compare_policy.py:493-523); policy_stride >= 1929 */
   const uint8_t* black_rows; /* nullable, [batch]: 1 = Black to move, the row goes through the rank-mirror table;
                               0 / null = White, identity (the reference alternates rows: first_is_white) */
+  int32_t* move_out;       /* nullable, [batch]: the move chosen from each policy row on the device, as an index
+                              into that row (model_bis.py:385-394: temperature 0 -> arg-max, else a draw from
+                              softmax(logits / T)). crl_forward needs policy_out as well (the rows it reads);
+                              crl_forward_host may leave policy_out null and then copies only the indices back */
+  const float* move_uniform; /* nullable, [batch] numbers in [0,1): the draw is the first index whose cumulative
+                              probability exceeds move_uniform[b] (the caller owns the random stream, so a run
+                              can be reproduced); null = arg-max (lowest index on ties) */
+  float move_temperature;  /* T above; 0 = arg-max */
 } crl_io;
 
 /* Constructor: replaces BT4.__init__ (value.py:122-153). The device must be a B200 (sm_100). */
@@ -216,6 +227,11 @@ int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t m
  * the board, a plane-109 value that is not min(c/100, 1) for an integer c, plane 110 not empty or plane 111
  * not all ones. */
 int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_t* packed);
+
+/* Legal-move bitsets on the device: `count` packed records (device memory, CRL_LAYOUT_PACKED104) -> bits
+ * [count, stride] (device memory, stride >= 233; bit m of a row = entry m of the 1858-move list legal in the
+ * mover's view, a knight promotion sets the plain from-to entry). Same rows as crl_playout_positions' legal1858. */
+int crl_legal_masks_packed104(crl_handle* h, const void* packed, int64_t count, uint8_t* bits, int64_t stride, void* stream);
 
 /* Move vocabulary (utils/vocab.py:9-438): writes the UCI string of entry `index` of the 1929-entry
  * list into buf (>= 16 bytes); entries < 1858 are the Leela list. Returns 0, or CRL_ERR_INVALID. */

@@ -103,3 +103,30 @@ def move_squares(uci):
 def legal_token(uci):
     """Vocabulary string of a legal move: knight promotions drop the 'n' (model_bis.py:376-379)."""
     return uci[:-1] if uci.endswith("n") else uci
+
+
+def choose_moves(rows, is_prob, temperature, uniforms=None):
+    """Test oracle for the on-device move choice (model_bis.py:385-394: temperature 0 -> arg-max, else a draw from
+    softmax(logits / T); the draw is made reproducible by taking the caller's uniform number through the
+    inverse CDF). rows: [B, V] logits, or probabilities with is_prob. Returns (index [B], margin [B]) where
+    margin is the relative distance of u * total from the nearest CDF step (a caller comparing against
+    another implementation may accept a neighbouring index when the margin is within rounding)."""
+    import numpy as np
+    rows = np.asarray(rows, dtype=np.float32)
+    B = rows.shape[0]
+    best = rows.argmax(axis=1)
+    if uniforms is None or temperature == 0:
+        return best.astype(np.int32), np.ones(B)
+    inv_t = np.float32(1.0 / temperature)
+    top = rows.max(axis=1, keepdims=True)
+    if is_prob:
+        w = np.where(rows > 0, np.power(np.maximum(rows, 0) / top, inv_t, dtype=np.float32), np.float32(0))
+    else:
+        w = np.exp((rows - top) * inv_t, dtype=np.float32)
+    cdf = np.cumsum(w.astype(np.float64), axis=1)
+    thr = np.asarray(uniforms, dtype=np.float32).astype(np.float64) * cdf[:, -1]
+    idx = (cdf > thr[:, None]).argmax(axis=1)
+    none = ~(cdf > thr[:, None]).any(axis=1)
+    idx[none] = best[none]
+    margin = np.abs(cdf - thr[:, None]).min(axis=1) / cdf[:, -1]
+    return idx.astype(np.int32), margin

@@ -348,6 +348,80 @@ def test_packed104_input_is_bit_identical_to_f16_planes():
         eng19.forward(packed.cuda(), layout="packed104")
 
 
+def test_move_choice_on_device_matches_oracle():
+    """Arg-max and inverse-CDF draws made on the GPU from the policy rows (logits and probabilities, f32 and f16,
+    temperatures 0 / 0.5 / 1 / 2, native and 1929-entry vocabulary) equal the numpy oracle applied to the rows
+    the same call returned; a draw may differ only where u * total sits within rounding of a CDF step. The host
+    entry point with policy=False returns the same indices while copying back 4 bytes per position."""
+    from chessrl_b200 import Engine, positions
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=61)
+    n = 300
+    pos = positions.playout_positions(n, seed=9, max_plies=100)
+    planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
+    eng = Engine(engine_cfg(cfg, chunk=128))
+    eng.load_state_dict(sd)
+    g = torch.Generator().manual_seed(5)
+    u = torch.rand(n, generator=g)
+    legal = np.unpackbits(pos["legal1858"].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool)
+    for softmax in (False, True):
+        for dtype in (torch.float32, torch.float16):
+            for temp in (0.0, 0.5, 1.0, 2.0):
+                for rl in (False, True):
+                    out = eng.forward(planes, legal_mask=bits, policy_softmax=softmax, policy_dtype=dtype, moves=True,
+                                      temperature=temp, uniforms=u.cuda(), rl_vocab=rl,
+                                      black_rows=pos["black"].cuda() if rl else None)
+                    rows = out["policy"].float().cpu().numpy()
+                    want, margin = vocab.choose_moves(rows, softmax, temp, u.numpy())
+                    got = out["move"].cpu().numpy()
+                    bad = got != want
+                    assert not (bad & (margin > 1e-5)).any(), (softmax, dtype, temp, rl, int(bad.sum()))
+                    assert bad.sum() <= 2
+                    if not rl and temp <= 1.0:
+                        assert legal[np.arange(n), got].all()          # a masked move is never chosen
+    am = eng.forward(planes, legal_mask=bits, moves=True)["move"].cpu()
+    assert torch.equal(am, eng.forward(planes, legal_mask=bits)["policy"].argmax(-1).int().cpu())
+    host = eng.forward(pos["planes112"].pin_memory(), legal_mask=pos["legal1858"], policy=False, wdl=False, host=True,
+                       policy_softmax=True, moves=True, temperature=1.0, uniforms=u)
+    dev = eng.forward(planes, legal_mask=bits, policy_softmax=True, policy_dtype=torch.float16, moves=True,
+                      temperature=1.0, uniforms=u.cuda())
+    assert set(host) == {"move"} and torch.equal(host["move"], dev["move"].cpu())
+    with pytest.raises(Exception):
+        eng.forward(planes, moves=True, temperature=-1.0)
+
+
+def test_legal_moves_generated_on_device_match_the_host_generator():
+    """Legal-move bitsets generated on the GPU from the packed records equal, bit for bit, the host generator's
+    (itself pinned by perft counts and the oracle) on 12 000 seeded playout positions up to 300 plies deep
+    (castling, en passant from the history planes, promotions, checks and pins all occur), and a forward pass
+    masking with them is bit-identical to one given the host bitsets."""
+    from chessrl_b200 import Engine, positions
+    cfg = bt4spec.SpecConfig.baseline(1, 256, 512, 8, smolgen=False)
+    eng = Engine(engine_cfg(cfg))
+    eng.load_state_dict(bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=71))
+    seen_ep = seen_castle = seen_promo = 0
+    for seed, plies in ((11, 300), (12, 120), (13, 40)):
+        n = 4000
+        pos = positions.playout_positions(n, seed=seed, max_plies=plies, fens=True)
+        packed = positions.pack_planes104(pos["planes112"])
+        got = eng.legal_masks(packed.cuda()).cpu()
+        want = pos["legal1858"]
+        bad = (got != want).any(dim=1).nonzero().flatten().tolist()
+        assert not bad, (seed, bad[:5], [pos["fens"][i] for i in bad[:5]])
+        bits = np.unpackbits(want.numpy(), axis=1, bitorder="little")[:, :1858]
+        seen_promo += int(bits[:, 1792:].any(axis=1).sum())
+        seen_ep += sum(1 for f in pos["fens"] if f.split()[3] != "-")
+        seen_castle += int((bits[:, vocab.policy_index.index("e1g1")] | bits[:, vocab.policy_index.index("e1c1")]).sum())
+    assert seen_ep > 0 and seen_castle > 0 and seen_promo > 0
+    pos = positions.playout_positions(200, seed=14, max_plies=150)
+    packed = positions.pack_planes104(pos["planes112"]).cuda()
+    a = eng.forward(packed, layout="packed104", legal_mask=pos["legal1858"].cuda(), policy_softmax=True)["policy"]
+    b = eng.forward(packed, layout="packed104", legal_mask="records", policy_softmax=True)["policy"]
+    assert torch.equal(a, b)
+    with pytest.raises(Exception):
+        eng.forward(pos["planes112"].cuda(), legal_mask="records")      # needs the packed layout
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""
