@@ -302,6 +302,23 @@ def main():
            "h2d_bytes_per_step": (planes_host.numel() * planes_host.element_size() + bits_host.numel()) * world,
            "d2h_bytes_per_step": ((0 if value_only else per_rank * 1858 * 2) + per_rank * 12) * world}
 
+    # the same call when the caller wants moves rather than distributions: legal moves generated on the GPU from
+    # the packed records, the move drawn on the GPU, 16 bytes per position back instead of the policy row
+    e2e_moves = None
+    if layout == "packed104" and not value_only:
+        uni = torch.rand(per_rank, generator=torch.Generator().manual_seed(rank)).pin_memory()
+
+        def step_host_moves():
+            return eng.forward(planes_host, layout=layout, legal_mask="records", policy=False, policy_softmax=True,
+                               moves=True, temperature=1.0, uniforms=uni, host=True)
+
+        step_host_moves()
+        ms_mv = timed(step_host_moves, args.steps) / args.steps
+        e2e_moves = {"value": wl["batch"] / (ms_mv * 1e-3), "unit": "positions/s",
+                     "h2d_bytes_per_step": (planes_host.numel() + 4 * per_rank) * world,
+                     "d2h_bytes_per_step": 16 * per_rank * world,
+                     "what": "host records in, legal masks + softmax + move draw on the GPU, move index + WDL out"}
+
     # per-kernel pass (untimed): CUDA events around every launch, on the launch stream
     eng.profile(True)
     step()
@@ -387,7 +404,7 @@ def main():
             "metric": "positions/sec", "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded random-playout positions, random-init weights)",
-            "config": config, "e2e": e2e,
+            "config": config, "e2e": e2e, "e2e_moves_only": e2e_moves,
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
             "latency_b256": latency, "batch_sweep_positions_per_s": sweep,
             "device_status": st}))

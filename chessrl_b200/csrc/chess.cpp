@@ -365,6 +365,73 @@ void planes112(const Board* hist, int n, int rule50, float* out) {
   }
 }
 
+// One move in the notation the reference's callers use: SAN ("Nbd7", "exd6", "O-O-O", "cxb8=N+", as read by
+// board.parse_san in Leela/pgn_to_input_data_decoder.py:24) or UCI ("g1f3", "c7b8n"). The text must select
+// exactly one legal move.
+bool parse_move_text(const Board& b, const std::string& text, Move& out) {
+  std::string t = text;
+  while (!t.empty() && (t.back() == '+' || t.back() == '#' || t.back() == '!' || t.back() == '?')) t.pop_back();
+  if (t.empty()) return false;
+  std::vector<Move> legal;
+  legal_moves(b, legal);
+  auto is_file = [](char c) { return c >= 'a' && c <= 'h'; };
+  auto is_rank = [](char c) { return c >= '1' && c <= '8'; };
+  if ((t.size() == 4 || t.size() == 5) && is_file(t[0]) && is_rank(t[1]) && is_file(t[2]) && is_rank(t[3])) {
+    for (const Move& m : legal)
+      if (uci(m) == t) { out = m; return true; }
+    if (t.size() == 5) return false;         // four characters may still be SAN ("axb5" is not, but stay strict below)
+  }
+  int piece = 1, promo = 0, to = -1, from_file = -1, from_rank = -1;
+  if (t == "O-O" || t == "0-0" || t == "O-O-O" || t == "0-0-0") {
+    const int home = b.side == 0 ? 4 : 60;
+    piece = 6; to = (t.size() == 3) ? home + 2 : home - 2; from_file = 4; from_rank = home >> 3;
+  } else {
+    size_t n = t.size();
+    static const std::string kPieces = "NBRQK";
+    if (n >= 2 && t[n - 2] == '=' && kPieces.find(t[n - 1]) != std::string::npos) { promo = static_cast<int>(kPieces.find(t[n - 1])) + 2; n -= 2; }
+    else if (n >= 3 && kPieces.find(t[n - 1]) != std::string::npos && is_rank(t[n - 2])) { promo = static_cast<int>(kPieces.find(t[n - 1])) + 2; n -= 1; }
+    if (promo == 6) return false;            // no promotion to a king
+    if (n < 2 || !is_file(t[n - 2]) || !is_rank(t[n - 1])) return false;
+    to = (t[n - 2] - 'a') + 8 * (t[n - 1] - '1');
+    size_t i = 0;
+    if (kPieces.find(t[0]) != std::string::npos) { piece = static_cast<int>(kPieces.find(t[0])) + 2; i = 1; }
+    for (; i + 2 < n; ++i) {
+      if (t[i] == 'x' || t[i] == '-') continue;
+      if (is_file(t[i]) && from_file < 0) from_file = t[i] - 'a';
+      else if (is_rank(t[i]) && from_rank < 0) from_rank = t[i] - '1';
+      else return false;
+    }
+  }
+  int found = 0;
+  for (const Move& m : legal) {
+    if (m.to != to || type_of(b.sq[m.from]) != piece || m.promo != promo) continue;
+    if (from_file >= 0 && file_of(m.from) != from_file) continue;
+    if (from_rank >= 0 && rank_of(m.from) != from_rank) continue;
+    out = m;
+    ++found;
+  }
+  return found == 1;
+}
+
+// hist[0] = current position, hist[1] = one ply earlier, ...: the packed record of planes112(hist, n, rule50)
+// written directly (same planes, same bytes as crl_pack_planes104 of that tensor).
+void pack_record(const Board* hist, int n, int rule50, uint8_t* rec) {
+  std::memset(rec, 0, CRL_PACKED104_BYTES);
+  const bool black = hist[0].side == 1;
+  for (int t = 0; t < 8 && t < n; ++t) {
+    const Board v = black ? mirror(hist[t]) : hist[t];
+    for (int s = 0; s < 64; ++s)
+      if (v.sq[s]) rec[(t * 13 + v.sq[s] - 1) * 8 + (s >> 3)] |= static_cast<uint8_t>(0x80u >> (s & 7));
+  }
+  const Board cur = black ? mirror(hist[0]) : hist[0];
+  rec[832] = (cur.castle & CWQ) ? 1 : 0;
+  rec[833] = (cur.castle & CWK) ? 1 : 0;
+  rec[834] = (cur.castle & CBQ) ? 1 : 0;
+  rec[835] = (cur.castle & CBK) ? 1 : 0;
+  rec[836] = black ? 1 : 0;
+  rec[837] = rule50 ? static_cast<uint8_t>(std::min<int>(hist[0].halfmove, 100)) : 0;
+}
+
 struct Rng {   // splitmix64
   uint64_t s;
   uint64_t next() {
@@ -475,6 +542,49 @@ int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_
         return CRL_ERR_INVALID;
       }
     }
+  }
+  return CRL_OK;
+}
+
+int crl_game_records(const char* moves, int32_t first_ply, int32_t count, int32_t rule50_plane, uint8_t* packed,
+                     uint8_t* black, uint8_t* legal1858, char* fens, int32_t* bad_move) {
+  if (bad_move != nullptr) *bad_move = -1;
+  if (moves == nullptr || first_ply < 0 || count < 0) return CRL_ERR_INVALID;
+  Board b;
+  start_position(b);
+  std::vector<Board> hist(1, b);
+  std::vector<std::string> toks;
+  {
+    std::string cur;
+    for (const char* p = moves;; ++p) {
+      if (*p == ' ' || *p == '\t' || *p == '\n' || *p == 0) {
+        if (!cur.empty()) { toks.push_back(cur); cur.clear(); }
+        if (*p == 0) break;
+      } else {
+        cur += *p;
+      }
+    }
+  }
+  if (count > 0 && static_cast<size_t>(first_ply) + static_cast<size_t>(count) - 1 > toks.size()) return CRL_ERR_INVALID;
+  auto emit = [&](int ply) {
+    const int j = ply - first_ply;
+    if (j < 0 || j >= count) return;
+    std::vector<Board> recent(hist.rbegin(), hist.rbegin() + std::min<size_t>(8, hist.size()));
+    if (packed != nullptr) pack_record(recent.data(), static_cast<int>(recent.size()), rule50_plane, packed + static_cast<size_t>(j) * CRL_PACKED104_BYTES);
+    if (black != nullptr) black[j] = static_cast<uint8_t>(b.side);
+    if (legal1858 != nullptr) legal_bits(b.side == 1 ? mirror(b) : b, legal1858 + static_cast<size_t>(j) * 233, 233);
+    if (fens != nullptr) std::snprintf(fens + static_cast<size_t>(j) * 96, 96, "%s", to_fen(b).c_str());
+  };
+  emit(0);
+  for (size_t i = 0; i < toks.size(); ++i) {
+    Move m;
+    if (!parse_move_text(b, toks[i], m)) {
+      if (bad_move != nullptr) *bad_move = static_cast<int32_t>(i);
+      return CRL_ERR_INVALID;
+    }
+    make_move(b, m);
+    hist.push_back(b);
+    emit(static_cast<int>(i) + 1);
   }
   return CRL_OK;
 }

@@ -81,3 +81,33 @@ def pack_planes104(planes, pin_memory=False):
     if rc != 0:
         raise L.CrlError(rc, "pack_planes104: a plane is not representable (piece planes 0/1, constant auxiliary planes)")
     return out
+
+
+def game_records(moves, first_ply=0, count=None, rule50_plane=True, legal=False, fens=False, pin_memory=False):
+    """Replay a game given as SAN or UCI move strings (the reference's `list_uci_to_input`,
+    Leela/pgn_to_input_data_decoder.py:14-78, parses SAN) and return packed records for the positions after
+    first_ply .. first_ply+count-1 moves, each with its history of up to 8 boards: dict with `packed` [count,840] u8,
+    `black` [count] u8 and optionally `legal1858` [count,233] and `fens`. Raises ValueError naming the first token
+    that does not select exactly one legal move."""
+    moves = list(moves)
+    if count is None:
+        count = len(moves) + 1 - first_ply
+    text = " ".join(moves).encode()
+    packed = torch.empty(count, L.PACKED104_BYTES, dtype=torch.uint8, pin_memory=pin_memory)
+    black = torch.empty(count, dtype=torch.uint8, pin_memory=pin_memory)
+    lg = torch.empty(count, 233, dtype=torch.uint8, pin_memory=pin_memory) if legal else None
+    fbuf = ctypes.create_string_buffer(96 * max(count, 1)) if fens else None
+    bad = ctypes.c_int32(-1)
+    rc = L.load().crl_game_records(text, first_ply, count, int(rule50_plane), packed.data_ptr(), black.data_ptr(),
+                                   lg.data_ptr() if legal else None, ctypes.addressof(fbuf) if fens else None,
+                                   ctypes.addressof(bad))
+    if rc != 0:
+        if bad.value >= 0:
+            raise ValueError(f"move {bad.value} ({moves[bad.value]!r}) does not select exactly one legal move")
+        raise L.CrlError(rc, "game_records")
+    out = {"packed": packed, "black": black}
+    if legal:
+        out["legal1858"] = lg
+    if fens:
+        out["fens"] = [fbuf.raw[i * 96:(i + 1) * 96].split(b"\0", 1)[0].decode() for i in range(count)]
+    return out

@@ -228,6 +228,15 @@ int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t m
  * not all ones. */
 int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_t* packed);
 
+/* Replays a game from the start position and emits the positions after first_ply .. first_ply+count-1 moves as
+ * packed records with their history of up to 8 boards - the input side of list_uci_to_input
+ * (Leela/pgn_to_input_data_decoder.py:14-78). `moves`: space-separated SAN (what the reference parses: board.parse_san,
+ * line 24) or UCI tokens; all of them are checked and played, so first_ply + count - 1 <= number of moves.
+ * Optional outputs: packed [count,840], black [count] (1 = Black to move), legal1858 [count,233], fens [count,96].
+ * A token that does not select exactly one legal move: CRL_ERR_INVALID and its index in *bad_move. */
+int crl_game_records(const char* moves, int32_t first_ply, int32_t count, int32_t rule50_plane, uint8_t* packed,
+                     uint8_t* black, uint8_t* legal1858, char* fens, int32_t* bad_move);
+
 /* Legal-move bitsets on the device: `count` packed records (device memory, CRL_LAYOUT_PACKED104) -> bits
  * [count, stride] (device memory, stride >= 233; bit m of a row = entry m of the 1858-move list legal in the
  * mover's view, a knight promotion sets the plain from-to entry). Same rows as crl_playout_positions' legal1858. */

@@ -422,6 +422,32 @@ def test_legal_moves_generated_on_device_match_the_host_generator():
         eng.forward(pos["planes112"].cuda(), legal_mask="records")      # needs the packed layout
 
 
+def test_policy_server_end_to_end_equals_direct_engine_call():
+    """The socket server (reference wire protocol) in front of a real engine: the arrays a client receives are the
+    engine's own rows for the same records - masked with GPU-generated legal moves, soft-maxed, scattered into the
+    1929 vocabulary with Black rows mirrored - and each row is a distribution over legal moves."""
+    from chessrl_b200 import Engine, positions, server
+    from test_server_cpu import SAN_A, UCI_B
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    eng = Engine(engine_cfg(cfg))
+    eng.load_state_dict(bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=81))
+    srv = server.PolicyServer(eng, port=0, linger_ms=1.0).start()
+    try:
+        req = [(SAN_A[:8], SAN_A[8:30]), (UCI_B[:9], UCI_B[9:])]
+        ans = server.query(srv.address, req)
+    finally:
+        srv.close()
+    assert len(ans) == 2
+    for (pre, post), rows in zip(req, ans):
+        g = positions.game_records(pre + post, first_ply=len(pre), count=len(post), legal=True)
+        direct = eng.forward(g["packed"].cuda(), layout="packed104", legal_mask=g["legal1858"].cuda(), policy_softmax=True,
+                             policy_dtype=torch.float16, rl_vocab=True, black_rows=g["black"].cuda())["policy"].cpu().numpy()
+        np.testing.assert_array_equal(rows, direct)
+        np.testing.assert_allclose(rows.astype(np.float32).sum(-1), 1.0, atol=2e-3)
+        legal = np.unpackbits(g["legal1858"].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool)
+        assert ((rows > 0).sum(-1) <= legal.sum(-1)).all()
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""
