@@ -28,7 +28,7 @@ EXPORTS = [
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
     "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
     "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static", "crl_perft", "crl_fen_to_planes19", "crl_legal_mask_1929",
-    "crl_playout_positions", "crl_pack_planes104", "crl_legal_masks_packed104", "crl_game_records",
+    "crl_playout_positions", "crl_pack_planes104", "crl_legal_masks_packed104", "crl_game_records", "crl_successors",
 ]
 
 
@@ -126,6 +126,8 @@ def load():
     lib.crl_legal_masks_packed104.restype = ctypes.c_int
     lib.crl_game_records.argtypes = [ctypes.c_char_p, i32, i32, i32, vp, vp, vp, vp, vp]
     lib.crl_game_records.restype = ctypes.c_int
+    lib.crl_successors.argtypes = [ctypes.c_char_p, i32, vp, vp, vp, vp]
+    lib.crl_successors.restype = ctypes.c_int
     lib.crl_vocab_move.argtypes = [ctypes.c_int, ctypes.c_char_p]
     lib.crl_vocab_move.restype = ctypes.c_int
     lib.crl_vocab_mirror_index.argtypes = [ctypes.c_int]

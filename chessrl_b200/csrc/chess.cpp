@@ -484,6 +484,23 @@ int crl_fen_to_planes19(const char* fen, float* out) {
   return CRL_OK;
 }
 
+int crl_successors(const char* fen, int32_t max_moves, char* ucis, char* fens, float* planes19_out, int32_t* count) {
+  Board b;
+  if (fen == nullptr || count == nullptr || max_moves < 0 || !parse_fen(fen, b)) return CRL_ERR_INVALID;
+  std::vector<Move> moves;
+  legal_moves(b, moves);
+  *count = static_cast<int32_t>(moves.size());
+  if (static_cast<int32_t>(moves.size()) > max_moves) return CRL_ERR_SHAPE;
+  for (size_t i = 0; i < moves.size(); ++i) {
+    Board c = b;
+    make_move(c, moves[i]);
+    if (ucis != nullptr) std::snprintf(ucis + i * 8, 8, "%s", uci(moves[i]).c_str());
+    if (fens != nullptr) std::snprintf(fens + i * 96, 96, "%s", to_fen(c).c_str());
+    if (planes19_out != nullptr) planes19(c, planes19_out + i * 64 * 19);
+  }
+  return CRL_OK;
+}
+
 int crl_legal_mask_1929(const char* fen, uint8_t* bits) {
   Board b;
   if (fen == nullptr || bits == nullptr || !parse_fen(fen, b)) return CRL_ERR_INVALID;

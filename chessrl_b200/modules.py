@@ -171,6 +171,44 @@ class BT4Planes19(BoardTransformer):
                          engine_device)
 
 
+    # -- value-driven move selection (new_paradigm/value.py:245-400) ------------------------------------
+    def get_batch_position_values(self, fens, device=None):
+        """FENs -> [B, 3] probabilities (black win, draw, white win), value.py:275-317."""
+        from . import positions
+        x = torch.stack([torch.from_numpy(positions.fen_to_tensor(f)) for f in fens]) if len(fens) else torch.empty(0, 8, 8, 19)
+        return self.position_values(x) if len(fens) else torch.empty(0, 3, device=self.engine().device)
+
+    def get_position_value(self, fen, device=None):
+        """One FEN -> [3] probabilities, value.py:245-273."""
+        return self.get_batch_position_values([fen])[0]
+
+    def calculate_move_values(self, fen, device=None):
+        """Every legal move with the mover's expected score of the position it leads to (0.5 * draw + own win),
+        all successors in one engine call (value.py:319-354). Returns (UCI strings, values [n] on the GPU)."""
+        from . import positions
+        ucis, _, planes = positions.successors(fen)
+        if not ucis:
+            return [], torch.empty(0, device=self.engine().device)
+        probs = self.position_values(planes)
+        white_to_move = fen.split()[1] == "w"
+        return ucis, 0.5 * probs[:, 1] + (probs[:, 2] if white_to_move else probs[:, 0])
+
+    def get_best_move_value(self, fen, T=1, device=None, return_probs=False, generator=None):
+        """value.py:356-400: T == 0 picks the highest-valued move, otherwise one draw from softmax(values / T)
+        (`generator`: optional torch.Generator on the engine's device for a reproducible draw)."""
+        ucis, values = self.calculate_move_values(fen)
+        if not ucis:
+            raise ValueError("No legal moves available")
+        if T == 0:
+            idx = int(torch.argmax(values))
+            probs = torch.zeros_like(values)
+            probs[idx] = 1.0
+        else:
+            probs = torch.softmax(values / T, dim=0)
+            idx = int(torch.multinomial(probs, num_samples=1, generator=generator))
+        return (ucis[idx], probs.cpu().numpy()) if return_probs else ucis[idx]
+
+
 class BT4Baseline(BoardTransformer):
     """The network of the target specification (smolgen bias, Mish FFN, 1858-move gather policy)."""
 

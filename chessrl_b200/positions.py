@@ -111,3 +111,22 @@ def game_records(moves, first_ply=0, count=None, rule50_plane=True, legal=False,
     if fens:
         out["fens"] = [fbuf.raw[i * 96:(i + 1) * 96].split(b"\0", 1)[0].decode() for i in range(count)]
     return out
+
+
+def successors(fen, planes19=True, pin_memory=False):
+    """Legal moves of `fen` (UCI strings, ordered by from-square, to-square, promotion) with the FENs and, optionally,
+    the 19-plane encodings [n,8,8,19] of the positions they lead to - the push / fen / pop loop of
+    calculate_move_values (new_paradigm/value.py:330-340) in one library call."""
+    n_max = 256
+    ubuf = ctypes.create_string_buffer(8 * n_max)
+    fbuf = ctypes.create_string_buffer(96 * n_max)
+    planes = torch.empty(n_max, 8, 8, 19, dtype=torch.float32, pin_memory=pin_memory) if planes19 else None
+    count = ctypes.c_int32(0)
+    rc = L.load().crl_successors(fen.encode(), n_max, ctypes.addressof(ubuf), ctypes.addressof(fbuf),
+                                 planes.data_ptr() if planes19 else None, ctypes.addressof(count))
+    if rc != 0:
+        raise L.CrlError(rc, "successors")
+    n = count.value
+    ucis = [ubuf.raw[i * 8:(i + 1) * 8].split(b"\0", 1)[0].decode() for i in range(n)]
+    fens = [fbuf.raw[i * 96:(i + 1) * 96].split(b"\0", 1)[0].decode() for i in range(n)]
+    return ucis, fens, (planes[:n] if planes19 else None)

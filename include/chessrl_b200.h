@@ -228,6 +228,12 @@ int crl_playout_positions(uint64_t seed, int64_t first, int64_t count, int32_t m
  * not all ones. */
 int crl_pack_planes104(const void* planes, int32_t layout, int64_t count, uint8_t* packed);
 
+/* The legal moves of `fen` (ordered by from-square, to-square, promotion piece) with the positions they lead to:
+ * the loop of calculate_move_values (new_paradigm/value.py:319-345: push, fen, pop for every legal move). Optional
+ * outputs: ucis [max_moves,8], fens [max_moves,96] (zero-terminated), planes19_out [max_moves,8,8,19] f32
+ * (fen_to_tensor of every successor). *count = number of legal moves; CRL_ERR_SHAPE if it exceeds max_moves. */
+int crl_successors(const char* fen, int32_t max_moves, char* ucis, char* fens, float* planes19_out, int32_t* count);
+
 /* Replays a game from the start position and emits the positions after first_ply .. first_ply+count-1 moves as
  * packed records with their history of up to 8 boards - the input side of list_uci_to_input
  * (Leela/pgn_to_input_data_decoder.py:14-78). `moves`: space-separated SAN (what the reference parses: board.parse_san,

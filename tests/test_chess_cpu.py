@@ -130,3 +130,26 @@ def test_packed104_records_round_trip_and_reject_unrepresentable_planes(lib):
     f32_exact = planes[:4].float()
     f32_exact.view(4, 64, 112)[:, :, 109] = torch.tensor([0.0, 0.07, 0.5, 1.0]).view(4, 1)
     assert positions.pack_planes104(f32_exact)[:, 837].tolist() == [0, 7, 50, 100]
+
+
+def test_successors_match_oracle(lib):
+    """Legal moves, resulting FENs and their 19-plane encodings of crl_successors against the oracle's rules, on
+    positions with promotions, castling, en passant, check and mate."""
+    from chessrl_b200 import positions
+    fens = [chesspos.START_FEN, KIWIPETE, ENDGAME, PROMO,
+            "rnbqkbnr/ppp1pppp/8/8/3pP3/8/PPPP1PPP/RNBQKBNR b KQkq e3 0 2",
+            "1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17"]
+    for fen in fens:
+        ucis, nxt, planes = positions.successors(fen)
+        pos = chesspos.Position(fen)
+        want = {}
+        for m in pos.legal_moves():
+            c = pos.copy()
+            c.push(m)
+            want[chesspos.uci(m)] = c
+        assert sorted(ucis) == sorted(want) and len(set(ucis)) == len(ucis)
+        assert planes.shape == (len(ucis), 8, 8, 19)
+        for u, f, p in zip(ucis, nxt, planes):
+            assert f == want[u].fen()
+            np.testing.assert_array_equal(p.numpy(), chesspos.planes19(want[u]))
+    assert positions.successors(fens[-1])[0] == []          # mate: nothing to choose from

@@ -448,6 +448,44 @@ def test_policy_server_end_to_end_equals_direct_engine_call():
         assert ((rows > 0).sum(-1) <= legal.sum(-1)).all()
 
 
+def test_value_driven_move_selection_matches_oracle():
+    """calculate_move_values / get_best_move_value of the 19-plane module (value.py:319-400): the mover's expected
+    score of every successor equals the FP32 oracle's within the WDL tolerance, T = 0 picks its arg-max, and a
+    seeded draw follows softmax(values / T)."""
+    from chessrl_b200 import BT4Planes19, positions
+    from oracle import chesspos
+    spec_cfg = bt4spec.SpecConfig.reference_value(2, 128, 192, 4)
+    spec = bt4spec.BT4Spec(spec_cfg)
+    sd = bt4spec.seeded_state_dict(spec, seed=91)
+    spec.load_state_dict(sd)
+    spec.eval()
+    model = BT4Planes19(2, 128, 192, 4)
+    model.load_state_dict(sd)
+    for fen in ("r3k2r/p1ppqpb1/bn2pnp1/3PN3/1p2P3/2N2Q1p/PPPBBPPP/R3K2R w KQkq - 0 1",
+                "rnbqkbnr/ppp1pppp/8/8/3pP3/8/PPPP1PPP/RNBQKBNR b KQkq e3 0 2"):
+        ucis, values = model.calculate_move_values(fen)
+        pos = chesspos.Position(fen)
+        planes = []
+        for u in ucis:
+            (m,) = [x for x in pos.legal_moves() if chesspos.uci(x) == u]
+            c = pos.copy()
+            c.push(m)
+            planes.append(torch.from_numpy(chesspos.planes19(c)))
+        with torch.no_grad():
+            probs = torch.softmax(spec.forward_all(torch.stack(planes).view(len(ucis), 64, 19))["wdl"], -1)
+        want = 0.5 * probs[:, 1] + (probs[:, 2] if fen.split()[1] == "w" else probs[:, 0])
+        assert (values.cpu() - want).abs().max() <= WDL_TOL
+        assert model.get_best_move_value(fen, T=0) == ucis[int(values.argmax())]
+        move, p = model.get_best_move_value(fen, T=0.5, return_probs=True,
+                                            generator=torch.Generator(device="cuda").manual_seed(3))
+        assert move in ucis and abs(float(p.sum()) - 1.0) < 1e-5
+        np.testing.assert_allclose(p, torch.softmax(values / 0.5, 0).cpu().numpy(), atol=1e-6)
+        one = model.get_position_value(fen).cpu()
+        assert one.shape == (3,) and abs(float(one.sum()) - 1.0) < 1e-4
+    with pytest.raises(ValueError):
+        model.get_best_move_value("1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17")
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""
