@@ -221,13 +221,15 @@ struct Workspace {
   __half *flat;     // [bc, 4096] policy scores (dense form)
   float* logits;    // [bc, 1929] f32 (dense form)
   __half *v2, *v2q;
-  uint8_t* legal;      // [bc, 236] legal-move bitsets generated from the packed records
+  uint8_t* legal;      // [batch, 236] legal-move bitsets generated from the packed records
   size_t total;
 };
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-Workspace carve(const crl_handle* h, char* base, int64_t bc) {
+// bc: positions per pass over the layers; total: positions of the whole call (the legal-move bitsets are
+// generated for all of them at once, before the first pass)
+Workspace carve(const crl_handle* h, char* base, int64_t bc, int64_t total) {
   const crl_config& c = h->cfg;
   const size_t M = static_cast<size_t>(bc) * 64;
   const size_t d = c.d_model;
@@ -267,7 +269,7 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc) {
   w.logits = reinterpret_cast<float*>(take((dense || lm) ? static_cast<size_t>(bc) * 2048 * 4 : 0));
   w.v2 = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
-  w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(bc) * 236 : 0));
+  w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(total) * 236 : 0));
   w.total = off;
   return w;
 }
@@ -657,14 +659,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     if (mask != nullptr && io->mask_mode == CRL_MASK_ADDITIVE) mask_row = mask + b0 * io->mask_stride * 4;
     int mask_mode = mask_row != nullptr ? io->mask_mode : CRL_MASK_NONE;
     long long mask_ld = io->mask_stride;
-    if (io->mask_mode == CRL_MASK_FROM_RECORDS) {
-      MoveGenParams mg{};
-      mg.recs = static_cast<const uint8_t*>(io->planes) + b0 * CRL_PACKED104_BYTES; mg.batch = bc;
-      mg.plain_idx = h->plain_idx; mg.bits = w.legal; mg.stride = 236;
-      legal_mask_packed104_kernel<<<static_cast<unsigned>((bc + 63) / 64), 64, 0, s>>>(mg);
-      CRL_CUDA(h, cudaGetLastError());
-      ++h->launches;
-      mask_row = w.legal; mask_mode = CRL_MASK_BITS; mask_ld = 236;
+    if (io->mask_mode == CRL_MASK_FROM_RECORDS) {   // generated for the whole call before the first pass
+      mask_row = w.legal + b0 * 236; mask_mode = CRL_MASK_BITS; mask_ld = 236;
     }
     float* out32 = io->policy_dtype == CRL_OUT_F32 ? static_cast<float*>(io->policy_out) + b0 * io->policy_stride : nullptr;
     __half* out16 = io->policy_dtype == CRL_OUT_F16 ? static_cast<__half*>(io->policy_out) + b0 * io->policy_stride : nullptr;
@@ -745,11 +741,20 @@ int run_batch(crl_handle* h, const crl_io* io, bool calib) {
   cudaStream_t s = static_cast<cudaStream_t>(io->stream);
   if (io->batch == 0) return CRL_OK;
   const int64_t chunk = std::min<int64_t>(h->chunk, io->batch);
-  const size_t need = carve(h, nullptr, chunk).total;
+  const size_t need = carve(h, nullptr, chunk, io->batch).total;
   if (io->workspace == nullptr || io->workspace_bytes < need)
     return fail(h, CRL_ERR_WORKSPACE, "workspace needs " + std::to_string(need) + " bytes");
   if ((reinterpret_cast<uintptr_t>(io->workspace) & 255) != 0) return fail(h, CRL_ERR_SHAPE, "workspace must be 256-byte aligned");
-  const Workspace w = carve(h, static_cast<char*>(io->workspace), chunk);
+  const Workspace w = carve(h, static_cast<char*>(io->workspace), chunk, io->batch);
+  if (io->mask_mode == CRL_MASK_FROM_RECORDS && io->policy_out != nullptr && !calib) {
+    // one thread per position: all positions of the call in one launch keep the whole GPU busy
+    MoveGenParams mg{};
+    mg.recs = static_cast<const uint8_t*>(io->planes); mg.batch = io->batch;
+    mg.plain_idx = h->plain_idx; mg.bits = w.legal; mg.stride = 236;
+    legal_mask_packed104_kernel<<<static_cast<unsigned>((io->batch + 63) / 64), 64, 0, s>>>(mg);
+    CRL_CUDA(h, cudaGetLastError());
+    ++h->launches;
+  }
   for (int64_t b0 = 0; b0 < io->batch; b0 += chunk) {
     const int64_t bc = std::min<int64_t>(chunk, io->batch - b0);
     const int rc = forward_chunk(h, io, b0, bc, w, calib, s);
@@ -1100,7 +1105,7 @@ int crl_finalize(crl_handle* h) {
 
 size_t crl_workspace_bytes(const crl_handle* h, int64_t batch) {
   if (h == nullptr || batch <= 0) return 0;
-  return carve(h, nullptr, std::min<int64_t>(h->chunk, batch)).total;
+  return carve(h, nullptr, std::min<int64_t>(h->chunk, batch), batch).total;
 }
 
 int crl_forward(crl_handle* h, const crl_io* io) {
