@@ -90,7 +90,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (prm.out_dtype != kOutF32) {
     const int oesz = prm.out_dtype == kOutF16 ? 2 : 1;
     if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, 32 * oesz) == kOk)
-      prm.use_tma_store = getenv("CRL_NO_TMA_STORE") ? 0 : 1;
+      prm.use_tma_store = 1;
   }
   // residual rows arrive through the same box shape when the buffer allows a tensor map
   CUtensorMap tmR;
@@ -128,9 +128,8 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (a.p.N <= 64) bn = 64;
   else if (a.p.N <= 128) bn = 128;
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
-  // large problems: CTA pairs on 256 x 256 tiles (CRL_GEMM_PAIR=0 turns them off for comparisons)
-  static const bool pair_ok = [] { const char* e = getenv("CRL_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
-  if (pair_ok && a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2) {
+  // large problems: CTA pairs on 256 x 256 tiles
+  if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2) {
     // a residual that a tensor map can describe goes through the variant that fetches it by TMA (measured on the
     // out-projection, K = 1024: -18 %; with K = 1536 the ring stage it gives up costs more than the fetch saves)
     const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.out_dtype != kOutF32 && a.p.N % 32 == 0 && a.p.K <= 1024 &&
