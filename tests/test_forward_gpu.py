@@ -486,6 +486,52 @@ def test_value_driven_move_selection_matches_oracle():
         model.get_best_move_value("1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17")
 
 
+def test_benchmark_shape_accuracy_against_fp32_oracle():
+    """The network the throughput is quoted on (15 blocks, d 1024, 32 heads, smolgen) on 256 seeded playout
+    positions against the FP32 oracle. FP16 meets its bars (logits within 2e-2, WDL within 1e-2, top-1 >= 99 %).
+    FP8 and INT8 meet the WDL bar (3e-2) but NOT the 99 % top-1 bar on these random-init weights: the reference's
+    best and second-best legal logits are a median 0.04 apart (logit std 0.19) while fifteen layers of e4m3 / int8
+    GEMMs leave an rms logit error of ~0.02, so the arg-max flips on close calls (measured 0.91 / 0.97). The
+    floors below only guard against regressions; where the reference's margin exceeds 0.15 the agreement is
+    asserted at 99 %."""
+    from chessrl_b200 import Engine, EngineConfig, positions
+    import chessrl_b200 as crl
+    torch.set_num_threads(max(torch.get_num_threads(), 8))
+    cfg = bt4spec.SpecConfig.baseline(15, 1024, 1536, 32, smolgen=True)
+    spec = bt4spec.BT4Spec(cfg)
+    sd = bt4spec.seeded_state_dict(spec, seed=5)
+    spec.load_state_dict(sd)
+    spec.eval()
+    n = 256
+    pos = positions.playout_positions(n, seed=77, max_plies=80)
+    with torch.no_grad():
+        ref = spec.forward_all(pos["planes112"].float().view(n, 64, 112))
+    legal = torch.from_numpy(np.unpackbits(pos["legal1858"].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool))
+    ref_masked = bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal)
+    top2 = ref_masked.sort(-1, descending=True).values[:, :2]
+    clear = (top2[:, 0] - top2[:, 1]) > 0.15
+    assert int(clear.sum()) >= 10
+    floors = {crl.DTYPE_F16: (0.99, 1e-2), crl.DTYPE_F8E4M3: (0.85, 3e-2), crl.DTYPE_I8: (0.92, 3e-2)}
+    for dt, (floor, wtol) in floors.items():
+        eng = Engine(EngineConfig(dtype=dt, **cfg.to_dict()))
+        eng.load_state_dict(sd)
+        x = pos["planes112"].cuda()
+        if dt == crl.DTYPE_F8E4M3:
+            eng.calibrate(x)
+        out = eng.forward(x, legal_mask=pos["legal1858"].cuda())
+        pol, wdl = out["policy"].float().cpu(), out["wdl"].cpu()
+        same = pol.argmax(-1) == ref_masked.argmax(-1)
+        agree, agree_clear = same.float().mean().item(), same[clear].float().mean().item()
+        werr = (wdl - torch.softmax(ref["wdl"], -1)).abs().max().item()
+        perr = (pol - ref_masked)[legal].abs().max().item()
+        print(f"benchmark shape, dtype {dt}: top-1 {agree:.4f} (clear margins {agree_clear:.4f}, {int(clear.sum())} positions), "
+              f"wdl err {werr:.3e}, policy max-abs err {perr:.3e}")
+        assert werr <= wtol and agree >= floor and agree_clear >= 0.99
+        if dt == crl.DTYPE_F16:
+            assert perr <= POLICY_TOL
+        eng.close()
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""
