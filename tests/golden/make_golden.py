@@ -163,7 +163,9 @@ def run_gpt_case(name, ref_root, seed):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference repository>")
+    ref_root = sys.argv[1]
     value_q, value = import_reference(ref_root)
     torch.set_num_threads(1)   # one thread: summation order independent of the machine
     run_case("ref_value_q_L2_d64_ff96_h2", value_q.BT4, bt4spec.SpecConfig.reference_value_q(2, 64, 96, 2),
