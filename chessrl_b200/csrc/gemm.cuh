@@ -77,17 +77,19 @@ struct GemmCfg {
   static constexpr uint32_t A_BYTES = BM * 128;
   static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = PAIR ? (RES ? 4 : 5) : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
+  // the residual variant fits five stages only without the per-column scale table (int8 keeps it and four stages)
+  static constexpr int STAGES = PAIR ? ((RES && KIND == kKindI8) ? 4 : 5) : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
+  static constexpr uint32_t TAB_BYTES = ((RES && KIND != kKindI8) ? 2 : 4) * BN * 4;   // bias [2][BN] (+ column scales [2][BN])
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
   // after the stages: the bias and column-scale tables [2][2][BN] f32, one 32-row x 64-byte staging tile per epilogue
   // warp (512-byte aligned: the TMA store swizzles by absolute address bits), one tile of the same shape per
   // warp for residual rows arriving by TMA, then the mbarriers (ring, accumulators, one per epilogue warp for
   // its residual tile) + TMEM slot
   static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
-  static constexpr uint32_t RES_OFF = EPI_OFF + 4 * BN * 4 + kEpiWarps * 2048;
+  static constexpr uint32_t RES_OFF = EPI_OFF + TAB_BYTES + kEpiWarps * 2048;
   static constexpr uint32_t BAR_OFF = RES_OFF + (RES ? kEpiWarps * 2048 : 0);
   static constexpr uint32_t USED_BYTES = BAR_OFF + 128 + kEpiWarps * 8;
-  static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + 896 /*alignment slack*/;
+  static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + (RES ? 768 : 896) /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
 };
 
@@ -302,7 +304,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int et = threadIdx.x - 64;        // 0..511 among the epilogue threads
     float* bias_s = reinterpret_cast<float*>(smem + Cfg::EPI_OFF);                  // [2][BN]
     float* cs_s = bias_s + 2 * BN;                                                  // [2][BN] per-column scales
-    const uint32_t stage_u = base + Cfg::EPI_OFF + 4 * BN * 4 + ew * 2048;          // 32 rows x 64 B
+    const uint32_t stage_u = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + ew * 2048;       // 32 rows x 64 B
     // 16-byte chunk q of staged row r; XOR swizzle keeps both access patterns bank-conflict free
     auto stage_off = [&](int r, int q) { return stage_u + r * 64 + ((q ^ ((r >> 1) & 3)) << 4); };
 

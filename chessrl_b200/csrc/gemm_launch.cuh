@@ -130,9 +130,8 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
   // large problems: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2) {
-    // a residual that a tensor map can describe goes through the variant that fetches it by TMA (measured on the
-    // out-projection, K = 1024: -18 %; with K = 1536 the ring stage it gives up costs more than the fetch saves)
-    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.out_dtype != kOutF32 && a.p.N % 32 == 0 && a.p.K <= 1024 &&
+    // a residual that a tensor map can describe goes through the variant that fetches it by TMA (out-projection: -18 %)
+    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.out_dtype != kOutF32 && a.p.N % 32 == 0 && (a.p.col_scale == nullptr || KIND == kKindI8) &&
                          a.p.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
     return res_tma ? gemm_launch_t<256, KIND, 1, 1>(a, num_sms, stream) : gemm_launch_t<256, KIND, 1, 0>(a, num_sms, stream);
   }

@@ -68,11 +68,16 @@ def send_message(sock, payload):
     sock.sendall(HEADER.pack(len(payload)) + payload)
 
 
+MAX_MESSAGE_BYTES = 256 << 20      # a length beyond this is treated as a broken peer, not as memory to reserve
+
+
 def recv_message(sock):
     head = recv_exact(sock, HEADER.size)
     if head is None:
         return None
     (n,) = HEADER.unpack(head)
+    if n > MAX_MESSAGE_BYTES:
+        return None
     return recv_exact(sock, n) if n else b""
 
 

@@ -110,6 +110,14 @@ def test_server_protocol_pooling_and_rejections(lib):
         np.testing.assert_array_equal(ok[0], expected_rows(SAN_A[:8], SAN_A[8:9]))
     finally:
         srv.close()
+    # a length prefix beyond the limit ends the connection instead of reserving the memory
+    import socket as _socket
+    import struct as _struct
+    a, b = _socket.socketpair()
+    a.sendall(_struct.pack(">Q", 1 << 60))
+    assert server.recv_message(b) is None
+    a.close()
+    b.close()
     # a pickle that names any global is refused before anything is called
     for evil in (pickle.dumps(os.getcwd), pickle.dumps([[["e4"], [print]]])):
         with pytest.raises(pickle.UnpicklingError):
