@@ -170,8 +170,9 @@ int crl_forward_host(crl_handle* h, const crl_io* io);
 #define CRL_STATIC_SCRATCH_BYTES (64u << 20)
 int crl_forward_static(crl_handle* h, const crl_io* io);
 
-/* Reads and clears the device status word (0 = fine, 101/102/103 = a bounded wait of the GEMM's
- * producer / MMA / epilogue role ran out). Synchronises the device. */
+/* Reads and clears the device status word (0 = fine; 101 / 102 / 103 = a bounded wait of the GEMM's producer /
+ * MMA / epilogue role ran out, 104 = shared memory less aligned than the GEMM's layout needs, 113 = a bounded wait
+ * of the attention kernel on its tile loads ran out). Synchronises the device. */
 int crl_last_status(crl_handle* h, int* device_status_word);
 /* Number of kernels the last crl_forward launched. */
 int64_t crl_last_launch_count(const crl_handle* h);
