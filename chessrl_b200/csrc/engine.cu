@@ -38,6 +38,8 @@ struct LayerW {
   int8_t *wqkv_q = nullptr, *wo_q = nullptr, *wff1_q = nullptr, *wff2_q = nullptr;
   float *cs_qkv = nullptr, *cs_o = nullptr, *cs_ff1 = nullptr, *cs_ff2 = nullptr;
   float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1, sa_qkv = 1;
+  // FP8: biases corrected for the mean effect of the weights' e4m3 rounding (filled by crl_calibrate)
+  float *bqkv8 = nullptr, *bo8 = nullptr, *bff1_8 = nullptr, *bff2_8 = nullptr;
 };
 
 struct ValueW {
@@ -63,6 +65,9 @@ struct crl_handle {
   std::vector<void*> allocs;
   std::string detail;
   int* status_dev = nullptr;
+  float* mean_dev = nullptr;          // [L][4][max(d, ff)] column sums of the four GEMM inputs over the calibration batch
+  float* mean_part = nullptr;         // [64][max(d, ff)] scratch of the column-sum kernel
+  long long mean_rows = 0;            // rows summed so far in this calibration call
   unsigned int* amax_dev = nullptr;   // [L*8] float bit patterns (5 taps per layer used)
   int64_t launches = 0;
   // optional per-kernel timing (crl_profile): event pairs around every launch, by category
@@ -363,6 +368,18 @@ int tap_amax(crl_handle* h, const __half* x, long long rows, int cols, int slot,
   return CRL_OK;
 }
 
+// calibration: add the column sums of x [rows, cols] to slot (layer, which) of mean_dev
+int tap_mean(crl_handle* h, const __half* x, long long rows, int cols, long long ld, int layer, int which, cudaStream_t s) {
+  if (h->mean_dev == nullptr) return CRL_OK;
+  const int wide = std::max(h->cfg.d_model, h->cfg.d_ff);
+  const int segments = 64;
+  colsum_f16_kernel<<<dim3((cols + 255) / 256, segments), 256, 0, s>>>(x, rows, cols, ld, h->mean_part, segments);
+  colsum_finish_kernel<<<(cols + 255) / 256, 256, 0, s>>>(h->mean_part, cols, segments,
+                                                          h->mean_dev + (static_cast<size_t>(layer) * 4 + which) * wide);
+  CRL_CUDA(h, cudaGetLastError());
+  return CRL_OK;
+}
+
 template <int NW>
 int attention_tma_launch_t(crl_handle* h, const AttnTmaParams& t, const CUtensorMap& tq, const CUtensorMap& tb,
                            const CUtensorMap& to, cudaStream_t s) {
@@ -500,10 +517,11 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       attn_in = w.xn;
     }
     if (calib && (rc = tap_amax(h, attn_in, M, d, l * 8 + 0, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_mean(h, attn_in, M, d, d, l, 0, s)) != CRL_OK) return rc;
     // QKV projection (attn.py:501-503 fused into one [3d, d] weight)
     {
       Lin q; q.m = M; q.n = 3 * d; q.k = d; q.c = w.t1; q.ldc = 3 * d; q.bias = L.bqkv;
-      if (f8) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); }
+      if (f8) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); q.bias = L.bqkv8; }
       if (qkv8) { q.out = kOutE4M3; q.out_scale = L.sa_qkv; }   // Q, K, V cross HBM as e4m3 (one scale for the three)
       else if (i8) { q.kind = kKindI8; q.a = w.x8; q.w = L.wqkv_q; q.row_scale = w.xs; q.col_scale = L.cs_qkv; }
       else { q.a = attn_in; q.w = L.wqkv; }
@@ -565,12 +583,13 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       ++h->launches;
     }
     if (calib && (rc = tap_amax(h, w.t2, M, d, l * 8 + 1, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_mean(h, w.t2, M, d, d, l, 1, s)) != CRL_OK) return rc;
     if (i8 && (rc = quant_rows_i8(h, w.t2, M, d, w.t2_8, w.t2s, s)) != CRL_OK) return rc;
     // out-proj + residual (+ LayerNorm for post-LN)
     {
       Lin o; o.m = M; o.n = d; o.k = d; o.bias = L.bo; o.res = w.x; o.ldr = d; o.lda = d; o.ldw = d;
       o.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; o.ldc = d;
-      if (f8) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); }
+      if (f8) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); o.bias = L.bo8; }
       else if (i8) { o.kind = kKindI8; o.a = w.t2_8; o.w = L.wo_q; o.row_scale = w.t2s; o.col_scale = L.cs_o; }
       else { o.a = w.t2; o.w = L.wo; }
       if ((rc = linear(h, o, s)) != CRL_OK) return rc;
@@ -584,20 +603,22 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       ffn_in = w.xn;
     }
     if (calib && (rc = tap_amax(h, ffn_in, M, d, l * 8 + 2, s)) != CRL_OK) return rc;
+    if (calib && (rc = tap_mean(h, ffn_in, M, d, d, l, 2, s)) != CRL_OK) return rc;
     // FFN (value.py:65-67: act after ff2; specification: act between)
     {
       Lin a; a.m = M; a.n = ff; a.k = d; a.bias = L.bff1; a.lda = d; a.ldw = d; a.ldc = ff;
       a.act = c.ffn_act_pos == CRL_FFN_ACT_MID ? act : kActNone;
-      if (f8) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; }
+      if (f8) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; a.bias = L.bff1_8; }
       else if (i8) { a.kind = kKindI8; a.a = w.x8; a.w = L.wff1_q; a.row_scale = w.xs; a.col_scale = L.cs_ff1; a.c = w.t1; }
       else { a.a = ffn_in; a.w = L.wff1; a.c = w.t1; }
       if ((rc = linear(h, a, s)) != CRL_OK) return rc;
       if (i8 && (rc = quant_rows_i8(h, w.t1, M, ff, w.t1_8, w.t1s, s)) != CRL_OK) return rc;
       if (calib && (rc = tap_amax(h, w.t1, M, ff, l * 8 + 3, s)) != CRL_OK) return rc;
+      if (calib && (rc = tap_mean(h, w.t1, M, ff, ff, l, 3, s)) != CRL_OK) return rc;
       Lin b; b.m = M; b.n = d; b.k = ff; b.bias = L.bff2; b.lda = ff; b.ldw = ff; b.res = w.x; b.ldr = d;
       b.act = c.ffn_act_pos == CRL_FFN_ACT_END ? act : kActNone;
       b.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; b.ldc = d;
-      if (f8) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); }
+      if (f8) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); b.bias = L.bff2_8; }
       else if (i8) { b.kind = kKindI8; b.a = w.t1_8; b.w = L.wff2_q; b.row_scale = w.t1s; b.col_scale = L.cs_ff2; }
       else { b.a = w.t1; b.w = L.wff2; }
       if ((rc = linear(h, b, s)) != CRL_OK) return rc;
@@ -787,6 +808,31 @@ int grow(crl_handle* h, T** p, size_t* have, size_t need) {
   CRL_CUDA(h, cudaMalloc(&q, need));
   *p = static_cast<T*>(q);
   *have = need;
+  return CRL_OK;
+}
+
+// FP8 bias correction. The e4m3 copy W' of a weight matrix differs from W by a fixed, known rounding error; for
+// inputs x its effect on the output is (W' - W) x, whose mean over the data is (W' - W) mean(x). Subtracting that
+// from the bias removes the coherent part of the weight-rounding error (on the benchmark network it is half of the
+// rms logit error) at no cost per call. mean(x) comes from the calibration pass: column sums of the four GEMM
+// inputs of every layer.
+int correct_fp8_biases(crl_handle* h, long long rows, cudaStream_t s) {
+  const crl_config& c = h->cfg;
+  const int d = c.d_model, ff = c.d_ff, L = c.n_layers, wide = std::max(d, ff);
+  const float inv_rows = 1.0f / static_cast<float>(rows);
+  auto run = [&](const __half* W, const uint8_t* W8, float mult, const float* colsum, const float* bias, float* out, int n_out, int k_in) {
+    bias_correct_kernel<<<(n_out + 7) / 8, 256, 0, s>>>(W, W8, 1.0f / mult, colsum, inv_rows, bias, out, n_out, k_in);
+  };
+  for (int l = 0; l < L; ++l) {
+    LayerW& Lw = h->layers[l];
+    const float* m = h->mean_dev + static_cast<size_t>(l) * 4 * wide;
+    run(Lw.wqkv, Lw.wqkv8, Lw.sw_qkv, m, Lw.bqkv, Lw.bqkv8, 3 * d, d);
+    run(Lw.wo, Lw.wo8, Lw.sw_o, m + wide, Lw.bo, Lw.bo8, d, d);
+    run(Lw.wff1, Lw.wff1_8, Lw.sw_ff1, m + 2 * wide, Lw.bff1, Lw.bff1_8, ff, d);
+    run(Lw.wff2, Lw.wff2_8, Lw.sw_ff2, m + 3 * wide, Lw.bff2, Lw.bff2_8, d, ff);
+  }
+  CRL_CUDA(h, cudaGetLastError());
+  CRL_CUDA(h, cudaStreamSynchronize(s));
   return CRL_OK;
 }
 
@@ -1040,6 +1086,10 @@ int crl_finalize(crl_handle* h) {
     }
     if (c.dtype == CRL_DTYPE_F8E4M3) {
       if ((rc = upload_e4m3(h, &L.wqkv8, &L.sw_qkv, wqkv.data(), wqkv.size())) != CRL_OK) return rc;
+      if ((rc = upload_f32(h, &L.bqkv8, bqkv.data(), 3 * d)) != CRL_OK) return rc;
+      if ((rc = upload_f32(h, &L.bo8, get(h, lkey(l, "attention.out_proj.bias"))->data(), d)) != CRL_OK) return rc;
+      if ((rc = upload_f32(h, &L.bff1_8, get(h, lkey(l, "ff1.bias"))->data(), ff)) != CRL_OK) return rc;
+      if ((rc = upload_f32(h, &L.bff2_8, get(h, lkey(l, "ff2.bias"))->data(), d)) != CRL_OK) return rc;
       const auto& wo = *get(h, lkey(l, "attention.out_proj.weight"));
       const auto& w1 = *get(h, lkey(l, "ff1.weight"));
       const auto& w2 = *get(h, lkey(l, "ff2.weight"));
@@ -1125,6 +1175,16 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int L = h->cfg.n_layers;
   CRL_CUDA(h, cudaMemsetAsync(h->amax_dev, 0, sizeof(unsigned int) * 8 * L, s));
+  const int wide = std::max(h->cfg.d_model, h->cfg.d_ff);
+  const bool correct = h->cfg.dtype == CRL_DTYPE_F8E4M3;
+  if (correct) {
+    if (h->mean_dev == nullptr) {
+      int rc0 = dev_alloc(h, &h->mean_dev, static_cast<size_t>(L) * 4 * wide);
+      if (rc0 == CRL_OK) rc0 = dev_alloc(h, &h->mean_part, static_cast<size_t>(64) * wide);
+      if (rc0 != CRL_OK) return rc0;
+    }
+    CRL_CUDA(h, cudaMemsetAsync(h->mean_dev, 0, sizeof(float) * L * 4 * wide, s));
+  }
   crl_io io{};
   io.planes = planes; io.layout = layout; io.batch = batch; io.workspace = workspace; io.workspace_bytes = workspace_bytes;
   io.stream = stream;
@@ -1142,6 +1202,7 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
     h->layers[l].sa_bias = mult(amax[l * 8 + 4]);
     h->layers[l].sa_qkv = mult(amax[l * 8 + 5]);
   }
+  if (correct && (rc = correct_fp8_biases(h, batch * 64, s)) != CRL_OK) return rc;
   h->calibrated = true;
   return CRL_OK;
 }

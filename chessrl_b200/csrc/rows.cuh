@@ -352,6 +352,46 @@ __global__ void absmax_f16_kernel(const __half* __restrict__ x, long long rows, 
   if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
 }
 
+// Column sums of an f16 matrix in a fixed order (calibration only): block (x = column group of 256, y = row
+// segment) adds its rows top to bottom into part[y][col]; colsum_finish_kernel adds the segments in order.
+__global__ void __launch_bounds__(256) colsum_f16_kernel(const __half* __restrict__ x, long long rows, int cols, long long ld,
+                                                         float* __restrict__ part, int segments) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  const long long per = (rows + segments - 1) / segments;
+  const long long r0 = per * blockIdx.y, r1 = r0 + per < rows ? r0 + per : rows;
+  float acc = 0.0f;
+  for (long long r = r0; r < r1; ++r) acc += __half2float(x[r * ld + c]);
+  part[static_cast<long long>(blockIdx.y) * cols + c] = acc;
+}
+__global__ void colsum_finish_kernel(const float* __restrict__ part, int cols, int segments, float* __restrict__ acc) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float t = 0.0f;
+  for (int s = 0; s < segments; ++s) t += part[static_cast<long long>(s) * cols + c];
+  acc[c] += t;        // accumulates over the passes of one calibration call (one launch at a time per stream)
+}
+
+// FP8 bias correction (calibration only): out[n] = bias[n] + sum_k (W[n,k] - W8[n,k] / mult) * colsum[k] / rows, one
+// warp per output row. W is the f16 copy of the weights, W8 their e4m3 copy (value * mult rounded).
+__global__ void __launch_bounds__(256) bias_correct_kernel(const __half* __restrict__ W, const uint8_t* __restrict__ W8, float inv_mult,
+                                                           const float* __restrict__ colsum, float inv_rows,
+                                                           const float* __restrict__ bias, float* __restrict__ out, int n_out, int k_in) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= n_out) return;
+  float acc = 0.0f;
+  for (int k = lane; k < k_in; k += 32) {
+    const size_t i = static_cast<size_t>(n) * k_in + k;
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw(W8[i], __NV_E4M3);
+    const float w8 = __half2float(*reinterpret_cast<const __half*>(&hr)) * inv_mult;
+    acc = fmaf(__half2float(W[i]) - w8, colsum[k] * inv_rows, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[n] = bias[n] + acc;
+}
+
 // f16 rows -> per-row symmetric int8 + scale (dynamic per-token activation quantisation); one warp per row,
 // cols a multiple of 8.
 __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const __half* __restrict__ x, long long rows, int cols,

@@ -138,7 +138,9 @@ const char* crl_required_key(const crl_handle* h, int i);
 int crl_finalize(crl_handle* h);
 
 /* FP8 only: per-tensor activation scales from a calibration batch (device pointer), the static
- * equivalent of the reference's delayed scaling recipe (pretrain_fp8.py:75-79: E4M3, margin 0). */
+ * equivalent of the reference's delayed scaling recipe (pretrain_fp8.py:75-79: E4M3, margin 0). The same pass
+ * measures the mean input of every FP8 GEMM and folds the mean effect of the weights' e4m3 rounding into the
+ * GEMM's bias (the FP16 / calibration path keeps the original biases). */
 int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t batch, void* workspace,
                   size_t workspace_bytes, void* stream);
 
