@@ -10,6 +10,14 @@ entry point (pinned host planes -> device, forward, policy/WDL -> host). The dom
 roofline is measured live with CUDA events around each GEMM launch in one extra, untimed pass.
 `--impl reference` times the CPU restatement of the reference forward (the reference's own module is
 PyTorch on CPU and is not on this machine) on the host cores, on a bounded sample.
+
+Small repeatable programs for a profiler capture (`-k regex:<kernel>`); they print timings, not the JSON line:
+    python bench.py --case gemm <kind> <M> <N> <K> <out> [act] [residual]
+        one linear layer through `crl_linear` (kind: 0 f16, 1 e4m3, 2 int8 operands; out: 0 f16, 1 f32, 2 e4m3):
+        three launches, then 20 more timed with CUDA events
+    python bench.py --case forward <f16|f8|i8> <positions> [chunk]
+        the BT4-shaped forward pass: plain timing of three passes, then one pass with the library's per-launch
+        CUDA events, grouped by kernel and shape
 """
 import argparse
 import json
@@ -43,6 +51,22 @@ def flops_per_position(L, d, ff, H, smolgen, P=112, policy=True):
     f_policy = (3 * 2 * 64 * d * d + 2 * 64 * 64 * d) if policy else 0
     f_value = 2 * 64 * d * 128 + 2 * 8192 * 128 + 2 * 128 * 3
     return 2 * 64 * P * d + L * layer + f_policy + f_value
+
+
+def shard_bounds(batch, world, rank):
+    """Contiguous slice (first, count) of a step's `batch` positions that `rank` of `world` processes: slices are
+    disjoint and cover the batch exactly; the first batch % world ranks take one position more."""
+    base, rem = divmod(batch, world)
+    return rank * base + min(rank, rem), base + (1 if rank < rem else 0)
+
+
+def max_over_ranks(ms, dist, device):
+    """The step time of the job: the slowest rank's device time (one all-reduce of a scalar, outside the timed
+    region). `dist` is torch.distributed or None for a single process."""
+    t = torch.tensor([float(ms)], device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 class ClockSampler(threading.Thread):
@@ -184,7 +208,103 @@ def cpu_reference_forward(wl, sample, steps, warmup):
     return sum(times) / len(times), cores
 
 
+def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
+    from chessrl_b200 import _lib
+    lib = _lib.load()
+    dev = "cuda"
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    if kind == 1:
+        a = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+        w = torch.randn(N, K, device=dev, generator=g).to(torch.float8_e4m3fn)
+    elif kind == 2:
+        a = torch.randint(-127, 128, (M, K), device=dev, generator=g, dtype=torch.int8)
+        w = torch.randint(-127, 128, (N, K), device=dev, generator=g, dtype=torch.int8)
+    else:
+        a = torch.randn(M, K, device=dev, generator=g).half()
+        w = torch.randn(N, K, device=dev, generator=g).half()
+    c = torch.empty(M, N, device=dev, dtype={0: torch.float16, 1: torch.float32, 2: torch.uint8}[out])
+    b = torch.randn(N, device=dev, generator=g)
+    r = torch.randn(M, N, device=dev, generator=g).half() if residual else None
+
+    def launch():
+        return lib.crl_linear(kind, a.data_ptr(), K, w.data_ptr(), K, c.data_ptr(), N, out, M, N, K, b.data_ptr(),
+                              r.data_ptr() if r is not None else None, N, 0.01, act, status.data_ptr(), None)
+
+    for _ in range(3):
+        rc = launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        rc = launch()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / launches * 1e3
+    print(f"gemm kind={kind} M={M} N={N} K={K} out={out} act={act} res={residual}: rc {rc} status {status[0].item()}  "
+          f"{us:.1f} us/launch  {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s", flush=True)
+    return 0 if rc == 0 and status[0].item() == 0 else 1
+
+
+def forward_case(which, B, chunk=0):
+    import collections
+    import chessrl_b200 as crl
+    from chessrl_b200 import synth
+    from chessrl_b200.modules import _param_shapes
+    dtype = {"f16": crl.DTYPE_F16, "f8": crl.DTYPE_F8E4M3, "i8": crl.DTYPE_I8}[which]
+    cfg = crl.EngineConfig.baseline(15, 1024, 1536, 32, smolgen=True, dtype=dtype, chunk=chunk)
+    eng = crl.Engine(cfg, 0)
+    eng.load_state_dict(synth.seeded_state_dict(_param_shapes(cfg), seed=0))
+    planes = synth.synthetic_planes(B, 112, seed=1).cuda()
+    bits = synth.synthetic_legal_bits(B).cuda()
+    if dtype == crl.DTYPE_F8E4M3:
+        eng.calibrate(planes[:2048])
+
+    def step():
+        eng.forward(planes, legal_mask=bits, policy_softmax=True, policy_dtype=torch.float16)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 3
+    print(f"forward {which} B={B} chunk={chunk}: {ms:.2f} ms/step, {B / ms * 1e3:.0f} pos/s")
+    eng.profile(True)
+    step()
+    agg = collections.OrderedDict()
+    for e in eng.profile_entries():
+        a = agg.setdefault((e["cat"], e["m"], e["n"], e["k"], e["kind"]), [0, 0.0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += e["ms"]
+        a[2] += e["flops"]
+        a[3] += e["bytes"]
+    tot = sum(a[1] for a in agg.values())
+    print(f"profiled total {tot:.2f} ms")
+    for (cat, m, n, k, kind), a in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        name = ["gemm", "attn", "ln", "policy"][cat]
+        tf = a[2] / a[1] / 1e9 if a[1] else 0.0
+        gb = a[3] / a[1] / 1e6 if a[1] else 0.0
+        print(f"{name:6s} M={m:7d} N={n:5d} K={k:5d} kind={kind} x{a[0]:3d}  {a[1]:8.3f} ms "
+              f"({a[1] / tot * 100:5.1f}%)  {tf:8.1f} TFLOP/s  {gb:8.1f} GB/s")
+    rc, st = eng.last_status()
+    print(f"device status {st}", flush=True)
+    return 0 if rc == 0 and st == 0 else 1
+
+
 def main():
+    if len(sys.argv) > 2 and sys.argv[1] == "--case":
+        argv = sys.argv[2:]
+        if argv[0] == "gemm" and len(argv) >= 6:
+            return gemm_case(*[int(x) for x in argv[1:8]])
+        if argv[0] == "forward" and len(argv) >= 3:
+            return forward_case(argv[1], int(argv[2]), int(argv[3]) if len(argv) > 3 else 0)
+        print(__doc__)
+        return 2
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -240,7 +360,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    per_rank = wl["batch"] // world
+    first_pos, per_rank = shard_bounds(wl["batch"], world, rank)
     dtype = DTYPES[wl["dtype"]]
     cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only, dtype=dtype, chunk=args.chunk)
     eng = crl.Engine(cfg, local_rank)
@@ -248,7 +368,7 @@ def main():
     # seeded random playouts of 0..80 plies from the start position (the workload's stated input distribution):
     # 112-plane history encoding + legal-move bitsets from the library's own move generator
     from chessrl_b200 import positions
-    pos = positions.playout_positions(per_rank, seed=20240607, first=rank * per_rank, max_plies=80, pin_memory=True)
+    pos = positions.playout_positions(per_rank, seed=20240607, first=first_pos, max_plies=80, pin_memory=True)
     planes_host, bits_host = pos["planes112"], pos["legal1858"]
     layout = "nhwc"
     if args.input == "packed104":
@@ -279,10 +399,7 @@ def main():
             fn()
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if dist is not None:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return max_over_ranks(e0.elapsed_time(e1), dist, dev)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -299,8 +416,8 @@ def main():
     step_host()
     ms_e2e = timed(step_host, args.steps) / args.steps
     e2e = {"value": wl["batch"] / (ms_e2e * 1e-3), "unit": "positions/s",
-           "h2d_bytes_per_step": (planes_host.numel() * planes_host.element_size() + bits_host.numel()) * world,
-           "d2h_bytes_per_step": ((0 if value_only else per_rank * 1858 * 2) + per_rank * 12) * world}
+           "h2d_bytes_per_step": (planes_host[0].numel() * planes_host.element_size() + bits_host.shape[1]) * wl["batch"],
+           "d2h_bytes_per_step": ((0 if value_only else 1858 * 2) + 12) * wl["batch"]}
 
     # the same call when the caller wants moves rather than distributions: legal moves generated on the GPU from
     # the packed records, the move drawn on the GPU, 16 bytes per position back instead of the policy row
@@ -315,8 +432,8 @@ def main():
         step_host_moves()
         ms_mv = timed(step_host_moves, args.steps) / args.steps
         e2e_moves = {"value": wl["batch"] / (ms_mv * 1e-3), "unit": "positions/s",
-                     "h2d_bytes_per_step": (planes_host.numel() + 4 * per_rank) * world,
-                     "d2h_bytes_per_step": 16 * per_rank * world,
+                     "h2d_bytes_per_step": (planes_host.shape[1] + 4) * wl["batch"],
+                     "d2h_bytes_per_step": 16 * wl["batch"],
                      "what": "host records in, legal masks + softmax + move draw on the GPU, move index + WDL out"}
 
     # per-kernel pass (untimed): CUDA events around every launch, on the launch stream
@@ -414,4 +531,4 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    sys.exit(main() or 0)

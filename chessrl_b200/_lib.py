@@ -26,7 +26,7 @@ VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
 EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
     "crl_calibrate", "crl_workspace_bytes", "crl_num_moves", "crl_forward", "crl_forward_host", "crl_last_status",
-    "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_vocab_move",
+    "crl_last_launch_count", "crl_error_detail", "crl_strerror", "crl_linear", "crl_linear_ex", "crl_vocab_move",
     "crl_vocab_mirror_index", "crl_profile", "crl_profile_read", "crl_profile_entry", "crl_forward_static", "crl_perft", "crl_fen_to_planes19", "crl_legal_mask_1929",
     "crl_playout_positions", "crl_pack_planes104", "crl_legal_masks_packed104", "crl_game_records", "crl_successors",
 ]
@@ -51,6 +51,22 @@ class IO(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("policy_vocab", ctypes.c_int32), ("black_rows", ctypes.c_void_p),
         ("move_out", ctypes.c_void_p), ("move_uniform", ctypes.c_void_p), ("move_temperature", ctypes.c_float),
+    ]
+
+
+class LinearArgs(ctypes.Structure):
+    """Mirror of `crl_linear_args` (include/chessrl_b200.h)."""
+    _fields_ = [
+        ("kind", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("a", ctypes.c_void_p), ("lda", ctypes.c_int64),
+        ("w", ctypes.c_void_p), ("ldw", ctypes.c_int64),
+        ("c", ctypes.c_void_p), ("ldc", ctypes.c_int64),
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("bias", ctypes.c_void_p),
+        ("residual", ctypes.c_void_p), ("ldr", ctypes.c_int64), ("res_mod", ctypes.c_int32),
+        ("alpha", ctypes.c_float), ("act", ctypes.c_int32), ("out_scale", ctypes.c_float),
+        ("row_scale", ctypes.c_void_p), ("col_scale", ctypes.c_void_p),
+        ("device_status", ctypes.c_void_p), ("stream", ctypes.c_void_p),
     ]
 
 
@@ -112,6 +128,8 @@ def load():
     lib.crl_linear.argtypes = [ctypes.c_int, vp, i64, vp, i64, vp, i64, ctypes.c_int, i64, i64, i64, vp, vp, i64,
                                ctypes.c_float, ctypes.c_int, vp, vp]
     lib.crl_linear.restype = ctypes.c_int
+    lib.crl_linear_ex.argtypes = [ctypes.POINTER(LinearArgs)]
+    lib.crl_linear_ex.restype = ctypes.c_int
     lib.crl_perft.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_uint64)]
     lib.crl_perft.restype = ctypes.c_int
     lib.crl_fen_to_planes19.argtypes = [ctypes.c_char_p, vp]

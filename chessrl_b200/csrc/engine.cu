@@ -108,6 +108,26 @@ int cuda_fail(crl_handle* h, cudaError_t e, const char* what) {
     if (e__ != cudaSuccess) return cuda_fail((h), e__, #expr);     \
   } while (0)
 
+// Makes the handle's device current for one entry point and puts the caller's device back on every return
+// path: frameworks read the current device from the runtime, so an entry point must not leave it changed.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+    ok = err == cudaSuccess;
+    if (prev == device) prev = -1;       // nothing to restore
+  }
+  ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+#define CRL_ON_DEVICE(h)                                            \
+  DeviceGuard guard__((h)->device);                                 \
+  if (!guard__.ok) return cuda_fail((h), guard__.err, "cudaSetDevice")
+
 std::string lkey(int l, const char* tail) { return "layers." + std::to_string(l) + "." + tail; }
 
 void build_required(crl_handle* h) {
@@ -758,7 +778,7 @@ int check_io(crl_handle* h, const crl_io* io) {
 }
 
 int run_batch(crl_handle* h, const crl_io* io, bool calib) {
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   cudaStream_t s = static_cast<cudaStream_t>(io->stream);
   if (io->batch == 0) return CRL_OK;
   const int64_t chunk = std::min<int64_t>(h->chunk, io->batch);
@@ -888,7 +908,8 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return CRL_ERR_CUDA;
   if (prop.major != 10) return CRL_ERR_UNSUPPORTED;   // the kernels are sm_100a only
-  if (cudaSetDevice(device) != cudaSuccess) return CRL_ERR_CUDA;
+  DeviceGuard guard(device);
+  if (!guard.ok) return CRL_ERR_CUDA;
   crl_handle* h = new crl_handle();
   h->cfg = c;
   h->device = device;
@@ -912,7 +933,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
 
 void crl_destroy(crl_handle* h) {
   if (h == nullptr) return;
-  cudaSetDevice(h->device);
+  DeviceGuard guard(h->device);
   for (void* p : h->allocs) cudaFree(p);
   for (auto& r : h->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
   for (void* p : {h->st_move, h->st_black, h->st_planes, h->st_mask, h->st_policy, h->st_wdl, h->st_q, h->st_ws})
@@ -930,7 +951,7 @@ int crl_set_weight(crl_handle* h, const char* key, const float* data, int64_t nu
   if (h == nullptr || key == nullptr || data == nullptr || numel <= 0) return CRL_ERR_INVALID;
   if (std::find(h->required.begin(), h->required.end(), key) == h->required.end())
     return fail(h, CRL_ERR_INVALID, std::string("unexpected key ") + key);
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   std::vector<float>& v = h->raw[key];
   v.resize(static_cast<size_t>(numel));
   CRL_CUDA(h, cudaMemcpy(v.data(), data, static_cast<size_t>(numel) * sizeof(float), cudaMemcpyDefault));
@@ -948,7 +969,7 @@ int crl_num_moves(const crl_handle* h) {
 
 int crl_finalize(crl_handle* h) {
   if (h == nullptr) return CRL_ERR_INVALID;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   const crl_config& c = h->cfg;
   const size_t d = c.d_model, ff = c.d_ff, H = c.n_heads, P = c.planes;
   // --- every key present with the right size ---
@@ -1171,7 +1192,9 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
   if (h == nullptr || planes == nullptr || batch <= 0) return CRL_ERR_INVALID;
   if (!h->finalized) return fail(h, CRL_ERR_NOT_FINALIZED, "crl_finalize has not run");
   if (layout < 0 || layout > CRL_LAYOUT_PACKED104) return fail(h, CRL_ERR_INVALID, "unknown plane layout");
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  if (layout == CRL_LAYOUT_PACKED104 && h->cfg.planes != 112) return fail(h, CRL_ERR_INVALID, "the packed layout holds 112 planes");
+  if (layout == CRL_LAYOUT_PACKED104 && (reinterpret_cast<uintptr_t>(planes) & 3) != 0) return fail(h, CRL_ERR_INVALID, "packed planes must be 4-byte aligned");
+  CRL_ON_DEVICE(h);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int L = h->cfg.n_layers;
   CRL_CUDA(h, cudaMemsetAsync(h->amax_dev, 0, sizeof(unsigned int) * 8 * L, s));
@@ -1212,7 +1235,7 @@ int crl_legal_masks_packed104(crl_handle* h, const void* packed, int64_t count, 
   if (!h->finalized) return fail(h, CRL_ERR_NOT_FINALIZED, "crl_finalize has not run");
   if (count < 0 || stride < 233 || (count > 0 && (packed == nullptr || bits == nullptr))) return fail(h, CRL_ERR_INVALID, "bad arguments");
   if (count == 0) return CRL_OK;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   MoveGenParams mg{};
   mg.recs = static_cast<const uint8_t*>(packed); mg.batch = count; mg.plain_idx = h->plain_idx; mg.bits = bits; mg.stride = stride;
   legal_mask_packed104_kernel<<<static_cast<unsigned>((count + 63) / 64), 64, 0, static_cast<cudaStream_t>(stream)>>>(mg);
@@ -1225,7 +1248,7 @@ int crl_forward_host(crl_handle* h, const crl_io* io) {
   if (rc != CRL_OK) return rc;
   h->launches = 0;
   if (io->batch == 0) return CRL_OK;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   cudaStream_t s = static_cast<cudaStream_t>(io->stream);
   const size_t B = static_cast<size_t>(io->batch);
   const size_t pb = plane_bytes(h, io->layout) * B;
@@ -1291,7 +1314,7 @@ int crl_forward_static(crl_handle* h, const crl_io* io) {
     return fail(h, CRL_ERR_WORKSPACE, "batch " + std::to_string(io->batch) + " needs " + std::to_string(need) +
                                           " bytes of scratch; the static scratch of crl_forward_static holds " +
                                           std::to_string(static_cast<size_t>(CRL_STATIC_SCRATCH_BYTES)));
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   if (g_static_scratch_addr[h->device] == nullptr) {
     // one-time set-up per device, with that device current
     void* ptr = nullptr;
@@ -1307,7 +1330,7 @@ int crl_forward_static(crl_handle* h, const crl_io* io) {
 
 int crl_last_status(crl_handle* h, int* device_status_word) {
   if (h == nullptr || device_status_word == nullptr) return CRL_ERR_INVALID;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   CRL_CUDA(h, cudaDeviceSynchronize());
   int st = 0;
   CRL_CUDA(h, cudaMemcpy(&st, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
@@ -1329,7 +1352,7 @@ int crl_profile_entry(crl_handle* h, int64_t index, int* category, double* ms, d
   if (h == nullptr || category == nullptr || ms == nullptr || flops == nullptr || bytes == nullptr || mnk_kind == nullptr)
     return CRL_ERR_INVALID;
   if (index < 0 || static_cast<size_t>(index) >= h->prof_used) return CRL_ERR_INVALID;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   const auto& r = h->prof[index];
   CRL_CUDA(h, cudaEventSynchronize(r.b));
   float t = 0.0f;
@@ -1341,7 +1364,7 @@ int crl_profile_entry(crl_handle* h, int64_t index, int* category, double* ms, d
 
 int crl_profile_read(crl_handle* h, int category, double* ms, double* flops, double* bytes, int64_t* launches) {
   if (h == nullptr || ms == nullptr || flops == nullptr || bytes == nullptr || launches == nullptr) return CRL_ERR_INVALID;
-  CRL_CUDA(h, cudaSetDevice(h->device));
+  CRL_ON_DEVICE(h);
   CRL_CUDA(h, cudaDeviceSynchronize());
   *ms = 0.0; *flops = 0.0; *bytes = 0.0; *launches = 0;
   for (size_t i = 0; i < h->prof_used; ++i) {
@@ -1354,22 +1377,34 @@ int crl_profile_read(crl_handle* h, int category, double* ms, double* flops, dou
   return CRL_OK;
 }
 
-int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw, void* c, int64_t ldc, int out_dtype,
-               int64_t m, int64_t n, int64_t k, const float* bias, const void* residual, int64_t ldr, float alpha,
-               int act, int* device_status, void* stream) {
-  if (kind < 0 || kind > 2 || out_dtype < 0 || out_dtype > 2 || act < 0 || act > 3) return CRL_ERR_INVALID;
-  if (m <= 0 || n <= 0 || k <= 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return CRL_ERR_INVALID;
+int crl_linear_ex(const crl_linear_args* x) {
+  if (x == nullptr) return CRL_ERR_INVALID;
+  if (x->kind < 0 || x->kind > 2 || x->out_dtype < 0 || x->out_dtype > 2 || x->act < 0 || x->act > 3) return CRL_ERR_INVALID;
+  if (x->m <= 0 || x->n <= 0 || x->k <= 0 || x->m > INT32_MAX || x->n > INT32_MAX || x->k > INT32_MAX || x->res_mod < 0)
+    return CRL_ERR_INVALID;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return CRL_ERR_CUDA;
   GemmArgs g;
-  g.kind = kind; g.A = a; g.lda = lda; g.W = w; g.ldw = ldw;
-  g.p.M = static_cast<int>(m); g.p.N = static_cast<int>(n); g.p.K = static_cast<int>(k);
-  g.p.C = c; g.p.ldc = ldc; g.p.out_dtype = out_dtype; g.p.bias = bias;
-  g.p.residual = static_cast<const __half*>(residual); g.p.ldr = ldr; g.p.res_mod = 0;
-  g.p.alpha = alpha; g.p.row_scale = nullptr; g.p.col_scale = nullptr; g.p.act = act; g.p.out_scale = 1.0f;
-  g.p.status = device_status;
-  return gemm_launch(g, sms, static_cast<cudaStream_t>(stream));
+  g.kind = x->kind; g.A = x->a; g.lda = x->lda; g.W = x->w; g.ldw = x->ldw;
+  g.p.M = static_cast<int>(x->m); g.p.N = static_cast<int>(x->n); g.p.K = static_cast<int>(x->k);
+  g.p.C = x->c; g.p.ldc = x->ldc; g.p.out_dtype = x->out_dtype; g.p.bias = x->bias;
+  g.p.residual = static_cast<const __half*>(x->residual); g.p.ldr = x->ldr; g.p.res_mod = x->res_mod;
+  g.p.alpha = x->alpha; g.p.row_scale = x->row_scale; g.p.col_scale = x->col_scale; g.p.act = x->act;
+  g.p.out_scale = x->out_dtype == kOutE4M3 ? x->out_scale : 1.0f;
+  g.p.status = x->device_status;
+  return gemm_launch(g, sms, static_cast<cudaStream_t>(x->stream));
+}
+
+int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw, void* c, int64_t ldc, int out_dtype,
+               int64_t m, int64_t n, int64_t k, const float* bias, const void* residual, int64_t ldr, float alpha,
+               int act, int* device_status, void* stream) {
+  crl_linear_args x{};
+  x.kind = kind; x.out_dtype = out_dtype; x.a = a; x.lda = lda; x.w = w; x.ldw = ldw; x.c = c; x.ldc = ldc;
+  x.m = m; x.n = n; x.k = k; x.bias = bias; x.residual = residual; x.ldr = ldr; x.res_mod = 0; x.alpha = alpha;
+  x.act = act; x.out_scale = 1.0f; x.row_scale = nullptr; x.col_scale = nullptr; x.device_status = device_status;
+  x.stream = stream;
+  return crl_linear_ex(&x);
 }
 
 int crl_vocab_move(int index, char* buf) {

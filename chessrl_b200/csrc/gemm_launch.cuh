@@ -65,14 +65,24 @@ struct GemmArgs {
   GemmParams p{};
 };
 
-template <int BN, int KIND, int PAIR = 0, int RES = 0>
+// box shape of the epilogue's stores (and of the residual slab): pairs 64 columns x 32 rows, single CTAs 32 x 32
+inline bool out_map_ok(const GemmParams& p) {
+  if (p.out_dtype == kOutF32) return false;
+  const int oesz = p.out_dtype == kOutF16 ? 2 : 1;
+  // a slab that sticks out of the matrix is clipped by the TMA unit in whole 16-byte pieces: the row length in
+  // bytes has to be a multiple of 16 for the clipping to be exact
+  return (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && (static_cast<uint64_t>(p.ldc) * oesz) % 16 == 0 &&
+         (static_cast<uint64_t>(p.N) * oesz) % 16 == 0;
+}
+
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, KIND, PAIR, RES>;
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -82,22 +92,25 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (rc != kOk) return rc;
   rc = make_tmap_2d(&tmB, a.W, Cfg::ESZ, a.p.K, a.p.N, a.ldw * Cfg::ESZ, PAIR ? BN / 2 : BN);
   if (rc != kOk) return rc;
-  // output tensor map for the epilogue's TMA stores: 32 rows x 32 columns per box
+  // output tensor map for the epilogue's TMA stores
   CUtensorMap tmC;
   GemmParams prm = a.p;
   prm.use_tma_store = 0;
   std::memset(&tmC, 0, sizeof(tmC));
+  constexpr int kBoxCols = PAIR ? 64 : 32;
   if (prm.out_dtype != kOutF32) {
     const int oesz = prm.out_dtype == kOutF16 ? 2 : 1;
-    if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, 32 * oesz) == kOk)
+    if (make_tmap_2d(&tmC, prm.C, oesz, prm.N, prm.M, static_cast<uint64_t>(prm.ldc) * oesz, 32, kBoxCols * oesz) == kOk)
       prm.use_tma_store = 1;
   }
-  // residual rows arrive through the same box shape when the buffer allows a tensor map
+  if (PAIR && !prm.use_tma_store) return kErrShape;   // the slab epilogue has no other way out
+  if (PAIR && (O8 != 0) != (prm.out_dtype == kOutE4M3)) return kErrInvalid;
+  // the residual slab arrives through the same box shape when the buffer allows a tensor map
   CUtensorMap tmR;
   std::memset(&tmR, 0, sizeof(tmR));
   prm.use_tma_res = 0;
-  if (RES != 0 && prm.residual != nullptr && prm.res_mod == 0 && prm.use_tma_store &&
-      make_tmap_2d(&tmR, prm.residual, 2, prm.N, prm.M, static_cast<uint64_t>(prm.ldr) * 2, 32, 64) == kOk)
+  if (RES != 0 && prm.residual != nullptr && prm.res_mod == 0 &&
+      make_tmap_2d(&tmR, prm.residual, 2, prm.N, prm.M, static_cast<uint64_t>(prm.ldr) * 2, 32, 128) == kOk)
     prm.use_tma_res = 1;
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
   if constexpr (PAIR) {
@@ -113,10 +126,10 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
   } else {
     const int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tn_kernel<BN, KIND, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
+    gemm_tn_kernel<BN, KIND, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
     return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
   }
 }
@@ -128,12 +141,14 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (a.p.N <= 64) bn = 64;
   else if (a.p.N <= 128) bn = 128;
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
-  // large problems: CTA pairs on 256 x 256 tiles
-  if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2) {
-    // a residual that a tensor map can describe goes through the variant that fetches it by TMA (out-projection: -18 %)
-    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.out_dtype != kOutF32 && a.p.N % 32 == 0 && (a.p.col_scale == nullptr || KIND == kKindI8) &&
-                         a.p.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
-    return res_tma ? gemm_launch_t<256, KIND, 1, 1>(a, num_sms, stream) : gemm_launch_t<256, KIND, 1, 0>(a, num_sms, stream);
+  // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
+  if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&
+      (a.p.col_scale == nullptr || KIND == kKindI8)) {
+    if (a.p.out_dtype == kOutE4M3) return gemm_launch_t<256, KIND, 1, 0, 1>(a, num_sms, stream);
+    // a residual that a tensor map can describe is fetched by TMA (out-projection, ff2)
+    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
+                         (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
+    return res_tma ? gemm_launch_t<256, KIND, 1, 1, 0>(a, num_sms, stream) : gemm_launch_t<256, KIND, 1, 0, 0>(a, num_sms, stream);
   }
   if (bn == 64) return gemm_launch_t<64, KIND>(a, num_sms, stream);
   if (bn == 128) return gemm_launch_t<128, KIND>(a, num_sms, stream);

@@ -67,6 +67,46 @@ _LAYOUT_OF = {
 }
 
 
+def check_rows(name, t, dev, rows, dtypes):
+    """Raise ValueError unless tensor `t` lives on the device type of `dev`, has `rows` rows and one of `dtypes`.
+    The library receives raw pointers and cannot see any of this: a host pointer or a short buffer handed to a
+    kernel would be an illegal address on the GPU."""
+    if not (hasattr(t, "device") and hasattr(t, "dtype") and hasattr(t, "shape")):
+        raise ValueError(f"{name} must be a tensor")
+    if t.device.type != dev.type or (dev.type == "cuda" and dev.index is not None and t.device.index != dev.index):
+        raise ValueError(f"{name} must live on {dev}, got {t.device}")
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} must have dtype {' or '.join(str(d) for d in dtypes)}, got {t.dtype}")
+    if t.dim() < 1 or t.shape[0] != rows:
+        raise ValueError(f"{name} must have {rows} rows, got shape {tuple(t.shape)}")
+
+
+def check_forward_inputs(planes, dev, batch, n_moves, legal_mask=None, mask_mode=None, black_rows=None, uniforms=None,
+                         rl_vocab=False):
+    """Every device / shape / dtype rule of Engine.forward's tensor arguments, checked before any pointer
+    reaches the library (no kernel has been launched when this raises)."""
+    if planes.device.type != dev.type or (dev.type == "cuda" and dev.index is not None and planes.device.index != dev.index):
+        raise ValueError(f"planes must live on {dev}")
+    if legal_mask is not None and not isinstance(legal_mask, str):
+        check_rows("legal_mask", legal_mask, dev, batch, (torch.uint8, torch.float32))
+        if legal_mask.dim() != 2:
+            raise ValueError("legal_mask must be [B, ceil(V/8)] uint8 or [B, V] float32")
+        bits = legal_mask.dtype == torch.uint8 if mask_mode is None else mask_mode == L.MASK_BITS
+        if bits != (legal_mask.dtype == torch.uint8):
+            raise ValueError("mask_mode does not match the dtype of legal_mask (bitset: uint8, additive: float32)")
+        need = (n_moves + 7) // 8 if bits else n_moves
+        if legal_mask.shape[1] < need:
+            raise ValueError(f"legal_mask rows hold {legal_mask.shape[1]} entries, the move list needs {need}")
+    if black_rows is not None and rl_vocab:
+        check_rows("black_rows", black_rows, dev, batch, (torch.uint8,))
+        if black_rows.numel() != batch:
+            raise ValueError("black_rows must be [B]")
+    if uniforms is not None:
+        check_rows("uniforms", uniforms, dev, batch, (torch.float32,))
+        if uniforms.numel() != batch:
+            raise ValueError(f"uniforms must be [B] on {dev}")
+
+
 class Engine:
     def __init__(self, cfg: EngineConfig, device=0):
         self.lib = L.load()
@@ -167,8 +207,11 @@ class Engine:
         planes = planes.contiguous()
         b = self._batch_of(planes, layout)
         dev = torch.device("cpu") if host else self.device
-        if planes.device.type != dev.type:
-            raise ValueError(f"planes must live on {dev}")
+        if black_rows is not None:
+            black_rows = black_rows.to(torch.uint8).contiguous()
+        if uniforms is not None:
+            uniforms = uniforms.to(torch.float32).contiguous()
+        check_forward_inputs(planes, dev, b, self.n_moves, legal_mask, mask_mode, black_rows, uniforms, rl_vocab)
         io = L.IO()
         io.planes = planes.data_ptr()
         io.layout = self._layout(planes, layout)
@@ -203,14 +246,10 @@ class Engine:
                 io.move_out = out["move"].data_ptr()
                 io.move_temperature = float(temperature)
                 if uniforms is not None:
-                    uniforms = uniforms.to(torch.float32).contiguous()
-                    if uniforms.device.type != dev.type or uniforms.numel() != b:
-                        raise ValueError(f"uniforms must be [B] on {dev}")
                     io.move_uniform = uniforms.data_ptr()
             if rl_vocab:
                 io.policy_vocab = L.VOCAB_RL1929
                 if black_rows is not None:
-                    black_rows = black_rows.to(torch.uint8).contiguous()
                     io.black_rows = black_rows.data_ptr()
         if wdl and self.cfg.value_mode != L.VALUE_NONE:
             out["wdl"] = torch.empty(b, 3, dtype=torch.float32, **kw)

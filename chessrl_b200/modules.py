@@ -6,6 +6,7 @@ The parameters are ordinary fp32 `nn.Parameter`s under the reference's names, so
 engine keeps its own repacked f16 / e4m3 device copies, refreshed whenever a parameter changed.
 Inference only: `compute_loss=True` (training) is not provided.
 """
+import numpy as np
 import torch
 import torch.nn as nn
 
@@ -96,6 +97,32 @@ def _attach(root, dotted, param):
     node.register_parameter(parts[-1], param)
 
 
+def move_from_policy(eng, planes, bits, mirrored, T, force_legal, return_probs, generator):
+    """Policy logits of one position, illegal moves pushed down by 999 (model_bis.py:373-383; knight promotions share
+    the un-suffixed token), then the arg-max for T == 0 or one draw from softmax(logits / T) (model_bis.py:385-392).
+    Mask, softmax and draw run on the GPU inside the engine call; `generator` (torch.Generator, CPU) makes the draw
+    reproducible. With return_probs the distribution [1, V] comes back too (one-hot for T == 0, where the
+    reference leaves it undefined)."""
+    from . import positions
+    if force_legal and not bool(bits.any()):
+        raise ValueError("No legal moves available")
+    u = torch.rand(1, generator=generator) if T != 0 else None
+    out = eng.forward(planes.to(eng.device), legal_mask=bits.to(eng.device) if force_legal else None, wdl=False,
+                      moves=True, temperature=float(T), uniforms=u.to(eng.device) if u is not None else None)
+    index = int(out["move"][0])
+    move = positions.vocab_move(index)
+    if mirrored:
+        move = positions.mirror_uci(move)
+    if not return_probs:
+        return move
+    if T == 0:
+        probs = torch.zeros_like(out["policy"])
+        probs[0, index] = 1.0
+    else:
+        probs = torch.softmax(out["policy"] / T, dim=-1)
+    return move, probs
+
+
 class BoardTransformer(nn.Module):
     """Board transformer behind the reference's module protocol. `engine_device` is the GPU index."""
 
@@ -153,6 +180,79 @@ class BoardTransformer(nn.Module):
         (value.py:275-317), which softmaxes the value logits (value.py:315)."""
         return self.infer(x, policy=False, wdl=True, wdl_softmax=softmax)["wdl"]
 
+    # -- move choice from the policy (model_bis.py:358-398, new_paradigm/value.py:214-243) ------------------
+    def _fen_inputs(self, fen):
+        """(planes [1,8,8,P] host tensor, legal bitset [1,242] over the 1929 vocabulary in the network's view,
+        whether the network sees the board rank-mirrored)."""
+        from . import positions
+        if self.cfg.planes == 19:
+            return (torch.from_numpy(positions.fen_to_tensor(fen))[None],
+                    torch.from_numpy(positions.legal_mask_1929(fen))[None], False)
+        # 112-plane networks see the board from the mover's side: mask and move are mirrored for Black
+        black = fen.split()[1] == "b"
+        view = positions.mirror_fen(fen) if black else fen
+        return (torch.from_numpy(positions.fen_to_planes112(fen))[None],
+                torch.from_numpy(positions.legal_mask_1929(view))[None], black)
+
+    def get_move_from_fen_no_thinking(self, fen, T=1, device="cuda", force_legal=True, return_probs=False,
+                                      generator=None):
+        """The reference's board-only move choice (new_paradigm/value.py:214-243), see `move_from_policy`.
+        112-plane networks see Black's positions rank-mirrored; the move returned is in real board coordinates
+        either way."""
+        if self.cfg.policy_mode != L.POLICY_DENSE4096:
+            raise ValueError("get_move_from_fen_no_thinking needs the 1929-move policy head")
+        planes, bits, mirrored = self._fen_inputs(fen)
+        return move_from_policy(self.engine(), planes, bits, mirrored, T, force_legal, return_probs, generator)
+
+    def _select_by_value(self, ucis, values, T, return_probs, generator):
+        """value.py:356-400 / value_q.py:349-397: arg-max for T == 0, else one draw from softmax(values / T)."""
+        if not ucis:
+            raise ValueError("No legal moves available")
+        if T == 0:
+            idx = int(torch.argmax(values))
+            probs = torch.zeros_like(values)
+            probs[idx] = 1.0
+        else:
+            probs = torch.softmax(values / T, dim=0)
+            idx = int(torch.multinomial(probs, num_samples=1, generator=generator))
+        return (ucis[idx], probs.cpu().numpy()) if return_probs else ucis[idx]
+
+    def get_best_move_value(self, fen, T=1, device=None, return_probs=False, generator=None):
+        """value.py:356-400: T == 0 picks the highest-valued move, otherwise one draw from softmax(values / T)
+        (`generator`: optional torch.Generator on the engine's device for a reproducible draw)."""
+        ucis, values = self.calculate_move_values(fen)
+        return self._select_by_value(ucis, values, T, return_probs, generator)
+
+    def calculate_move_values(self, fen, device=None):
+        """Every legal move of `fen` with the mover's value of the position it leads to, all successors in one
+        engine call. Returns (UCI strings, values [n] on the GPU)."""
+        return self.calculate_move_values_many([fen])[0]
+
+    def calculate_move_values_many(self, fens):
+        """The evaluation loops of metrics/tactics_evaluation_improved.py:8-62 and metrics/endgame_evaluation.py:6-63
+        call calculate_move_values once per position; this entry scores the successors of MANY positions in one
+        engine call. Returns a list of (UCI strings, values [n_i] on the GPU), one per FEN, values as
+        calculate_move_values defines them for this class."""
+        from . import positions
+        per, planes = [], []
+        for fen in fens:
+            ucis, succ_fens, p19 = positions.successors(fen, planes19=self.cfg.planes == 19)
+            if self.cfg.planes != 19 and ucis:
+                p19 = torch.from_numpy(np.stack([positions.fen_to_planes112(f) for f in succ_fens]))
+            per.append((ucis, fen.split()[1] == "w"))
+            if ucis:
+                planes.append(p19)
+        dev = self.engine().device
+        if not planes:
+            return [([], torch.empty(0, device=dev)) for _ in per]
+        values = self._successor_values(torch.cat(planes))
+        out, at = [], 0
+        for ucis, white in per:
+            v = values[at:at + len(ucis)]
+            at += len(ucis)
+            out.append((ucis, self._mover_value(v, white)))
+        return out
+
 
 class BT4(BoardTransformer):
     """`BT4(num_layers, d_model, d_ff, num_heads)` of new_paradigm/value_q.py:121-153: 112 input
@@ -161,6 +261,30 @@ class BT4(BoardTransformer):
     def __init__(self, num_layers=10, d_model=512, d_ff=736, num_heads=8, dtype=L.DTYPE_F16, engine_device=0):
         super().__init__(EngineConfig.reference_value_q(num_layers, d_model, d_ff, num_heads, dtype=dtype),
                          engine_device)
+
+    # -- Q-value entry points (new_paradigm/value_q.py:244-347). The reference feeds `fen_to_tensor`'s 19 planes
+    # into this class's 112-plane input layer there, which cannot run; the 112-plane encoding of the FEN with an
+    # empty history (positions.fen_to_planes112) takes their place.
+    def get_batch_position_values(self, fens, device=None):
+        """FENs -> [B, 1] tanh Q of `value_head_q` (value_q.py:275-310)."""
+        from . import positions
+        dev = self.engine().device
+        if len(fens) == 0:
+            return torch.empty(0, 1, device=dev)
+        x = torch.from_numpy(np.stack([positions.fen_to_planes112(f) for f in fens]))
+        return self.infer(x, policy=False, wdl=False, q=True)["q"].view(-1, 1)
+
+    def get_position_value(self, fen, device=None):
+        """One FEN -> scalar tanh Q (value_q.py:244-273)."""
+        return self.get_batch_position_values([fen]).squeeze()
+
+    def _successor_values(self, planes):
+        return self.infer(planes, policy=False, wdl=False, q=True)["q"].view(-1)
+
+    @staticmethod
+    def _mover_value(q, white_to_move):
+        """value_q.py:338-347: the mover's value of a successor is -Q for White to move, +Q for Black."""
+        return -q if white_to_move else q
 
 
 class BT4Planes19(BoardTransformer):
@@ -182,31 +306,13 @@ class BT4Planes19(BoardTransformer):
         """One FEN -> [3] probabilities, value.py:245-273."""
         return self.get_batch_position_values([fen])[0]
 
-    def calculate_move_values(self, fen, device=None):
-        """Every legal move with the mover's expected score of the position it leads to (0.5 * draw + own win),
-        all successors in one engine call (value.py:319-354). Returns (UCI strings, values [n] on the GPU)."""
-        from . import positions
-        ucis, _, planes = positions.successors(fen)
-        if not ucis:
-            return [], torch.empty(0, device=self.engine().device)
-        probs = self.position_values(planes)
-        white_to_move = fen.split()[1] == "w"
-        return ucis, 0.5 * probs[:, 1] + (probs[:, 2] if white_to_move else probs[:, 0])
+    def _successor_values(self, planes):
+        return self.position_values(planes)
 
-    def get_best_move_value(self, fen, T=1, device=None, return_probs=False, generator=None):
-        """value.py:356-400: T == 0 picks the highest-valued move, otherwise one draw from softmax(values / T)
-        (`generator`: optional torch.Generator on the engine's device for a reproducible draw)."""
-        ucis, values = self.calculate_move_values(fen)
-        if not ucis:
-            raise ValueError("No legal moves available")
-        if T == 0:
-            idx = int(torch.argmax(values))
-            probs = torch.zeros_like(values)
-            probs[idx] = 1.0
-        else:
-            probs = torch.softmax(values / T, dim=0)
-            idx = int(torch.multinomial(probs, num_samples=1, generator=generator))
-        return (ucis[idx], probs.cpu().numpy()) if return_probs else ucis[idx]
+    @staticmethod
+    def _mover_value(probs, white_to_move):
+        """value.py:345-352: 0.5 * draw + the mover's own win probability."""
+        return 0.5 * probs[:, 1] + (probs[:, 2] if white_to_move else probs[:, 0])
 
 
 class BT4Baseline(BoardTransformer):
@@ -339,6 +445,18 @@ class GPT(nn.Module):
         (`logits + (1-mask)*(-999)`, model_bis.py:383) and soft-maxed."""
         eng = self.engine()
         return eng.forward(board.to(eng.device), legal_mask=legal_mask, policy_softmax=softmax, wdl=False)["policy"]
+
+    def get_move_from_fen_no_thinking(self, fen, T=1, device="cuda", force_legal=True, return_probs=False,
+                                      generator=None):
+        """model_bis.py:358-398: last-token logits of the encoded board, `logits + (1 - mask) * -999`, arg-max for
+        T == 0 or one draw from softmax(logits / T); returns the UCI string (and the distribution [1, vocab])."""
+        from . import positions
+        if self.config.vocab_size < 1929:
+            raise ValueError("the legal-move mask spans the 1929-move vocabulary")
+        bits = torch.zeros(1, (self.config.vocab_size + 7) // 8, dtype=torch.uint8)
+        bits[0, :242] = torch.from_numpy(positions.legal_mask_1929(fen))
+        planes = torch.from_numpy(positions.fen_to_tensor(fen))[None]
+        return move_from_policy(self.engine(), planes, bits, False, T, force_legal, return_probs, generator)
 
     def forward(self, batch, compute_loss=False):
         """batch = (board [B,8,8,19], idx [B,0]) -> (logits [B,1,V], None, targets [B,64]) as model_bis.py:171-199."""

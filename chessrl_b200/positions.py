@@ -26,6 +26,57 @@ def fen_to_tensor(fen):
     return out
 
 
+def fen_to_planes112(fen, rule50_plane=False):
+    """One FEN -> [8, 8, 112] float16 planes of the 112-plane networks in the mover's view with an EMPTY history
+    (only the newest of the eight board slots is filled): 12 piece planes (mover's P N B R Q K, then the
+    opponent's; board rank-mirrored when Black is to move), castling planes 104..107 (ours O-O-O, ours O-O, theirs
+    O-O-O, theirs O-O), plane 108 = Black to move, plane 109 = halfmove/100 if `rule50_plane`, plane 111 = ones -
+    the plane semantics of Leela/gen_TC.py:42-59, 255-319 and Leela/ustotheirs.py:4-23. A FEN carries no earlier
+    boards, so slots 1..7 stay empty, as for the first position of a game."""
+    t = fen_to_tensor(fen)                            # [8, 8, 19], row 0 = rank 8, white pieces first
+    black = t[0, 0, 12] == 0.0
+    out = np.zeros((8, 8, 112), dtype=np.float16)
+    if black:
+        out[:, :, 0:6] = t[:, :, 6:12]                # mirrored ranks: row r of the view is row r of the rank-8-first tensor
+        out[:, :, 6:12] = t[:, :, 0:6]
+        cast = (t[0, 0, 17], t[0, 0, 16], t[0, 0, 15], t[0, 0, 14])     # q k Q K
+    else:
+        out[:, :, 0:12] = t[::-1, :, 0:12]
+        cast = (t[0, 0, 15], t[0, 0, 14], t[0, 0, 17], t[0, 0, 16])     # Q K q k
+    for i, c in enumerate(cast):
+        out[:, :, 104 + i] = c
+    out[:, :, 108] = 1.0 if black else 0.0
+    if rule50_plane:
+        out[:, :, 109] = t[0, 0, 18]
+    out[:, :, 111] = 1.0
+    return out
+
+
+def mirror_uci(uci):
+    """Rank-mirror a UCI move string (e2e4 <-> e7e5): the change of view between White's and Black's board."""
+    return "".join(str(9 - int(c)) if c.isdigit() else c for c in uci)
+
+
+def mirror_fen(fen):
+    """The same position seen from the other side: ranks flipped, colours, side to move, castling rights and the
+    en-passant square swapped with them."""
+    f = fen.split()
+    board = "/".join(r.swapcase() for r in reversed(f[0].split("/")))
+    side = "w" if f[1] == "b" else "b"
+    cast = "".join(sorted(f[2].swapcase(), key="KQkq".index)) if f[2] != "-" else "-"
+    ep = mirror_uci(f[3]) if f[3] != "-" else "-"
+    return " ".join([board, side, cast, ep] + f[4:])
+
+
+def vocab_move(index):
+    """Entry `index` of the reference's 1929-move policy vocabulary (utils/vocab.py `policy_index`) as a UCI string."""
+    buf = ctypes.create_string_buffer(16)
+    rc = L.load().crl_vocab_move(int(index), buf)
+    if rc != 0:
+        raise L.CrlError(rc, f"vocabulary index {index}")
+    return buf.value.decode()
+
+
 def legal_mask_1929(fen):
     """uint8 bitset [242] over the 1929 vocabulary (bit m little-endian in byte m//8)."""
     out = np.zeros(242, dtype=np.uint8)

@@ -81,8 +81,10 @@ def recv_message(sock):
     return recv_exact(sock, n) if n else b""
 
 
-def records_for(pairs, rule50_plane=True):
-    """Packed records, Black flags and per-pair position counts of a decoded request."""
+def records_for(pairs, rule50_plane=False):
+    """Packed records, Black flags and per-pair position counts of a decoded request. rule50_plane=False leaves
+    plane 109 empty, as the reference server's input does (Leela/ustotheirs.py:13-17 appends a blank plane there);
+    True writes halfmove/100 for networks trained on lc0 records."""
     packed, black, counts = [], [], []
     for pre, post in pairs:
         if len(pre) + 1 < 8:
@@ -103,7 +105,7 @@ class PolicyServer:
     """`engine`: a chessrl_b200.Engine with the 112-plane gather head (or any object with the same
     forward(packed, layout=..., host=True, ...) -> {"policy": [B,1929] f16 tensor} call)."""
 
-    def __init__(self, engine, host="127.0.0.1", port=65432, max_positions=2048, linger_ms=2.0, rule50_plane=True):
+    def __init__(self, engine, host="127.0.0.1", port=65432, max_positions=2048, linger_ms=2.0, rule50_plane=False):
         self.engine = engine
         self.max_positions = max_positions
         self.linger = linger_ms * 1e-3

@@ -199,6 +199,30 @@ int crl_linear(int kind, const void* a, int64_t lda, const void* w, int64_t ldw,
                int out_dtype, int64_t m, int64_t n, int64_t k, const float* bias, const void* residual,
                int64_t ldr, float alpha, int act, int* device_status, void* stream);
 
+/* The same operator with every epilogue term the engine's quantised paths use (one nn.Linear under the
+ * per-tensor FP8 recipe of model_fp8.py:43-45 / pretrain_fp8.py:75-79, or its W8A8 twin):
+ *   C = out_scale * ( act( alpha * row_scale[m] * col_scale[n] * (A W^T)[m,n] + bias[n] ) + residual[m % res_mod, n] )
+ * row_scale [M] and col_scale [N] f32 are nullable (per-token / per-output-channel de-quantisation); res_mod 0 means
+ * residual[m, n]; out_scale applies to e4m3 outputs only (the next GEMM's input multiplier). */
+typedef struct crl_linear_args {
+  int32_t kind;            /* CRL_DTYPE_* of A and W */
+  int32_t out_dtype;       /* 0 f16, 1 f32, 2 e4m3 */
+  const void* a; int64_t lda;
+  const void* w; int64_t ldw;
+  void* c; int64_t ldc;
+  int64_t m, n, k;
+  const float* bias;
+  const void* residual; int64_t ldr; int32_t res_mod;
+  float alpha;
+  int32_t act;             /* 0 none, 1 GELU, 2 Mish, 3 ReLU */
+  float out_scale;
+  const float* row_scale;
+  const float* col_scale;
+  int* device_status;      /* >= 4 ints of device memory, zero before the call */
+  void* stream;
+} crl_linear_args;
+int crl_linear_ex(const crl_linear_args* args);
+
 /* ---- host-side input producers (no GPU needed) ------------------------------------------------------------
  * The reference builds its inputs with python-chess; these entry points are the library's own rules
  * implementation (validated by perft counts and against the test oracle). */

@@ -439,7 +439,7 @@ def test_policy_server_end_to_end_equals_direct_engine_call():
         srv.close()
     assert len(ans) == 2
     for (pre, post), rows in zip(req, ans):
-        g = positions.game_records(pre + post, first_ply=len(pre), count=len(post), legal=True)
+        g = positions.game_records(pre + post, first_ply=len(pre), count=len(post), legal=True, rule50_plane=False)
         direct = eng.forward(g["packed"].cuda(), layout="packed104", legal_mask=g["legal1858"].cuda(), policy_softmax=True,
                              policy_dtype=torch.float16, rl_vocab=True, black_rows=g["black"].cuda())["policy"].cpu().numpy()
         np.testing.assert_array_equal(rows, direct)

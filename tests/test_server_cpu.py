@@ -74,7 +74,8 @@ class StandInEngine:
 
 def expected_rows(pre, post):
     from chessrl_b200 import positions
-    g = positions.game_records(pre + post, first_ply=len(pre), count=len(post))
+    g = positions.game_records(pre + post, first_ply=len(pre), count=len(post), rule50_plane=False)   # the server's default
+    assert int(g["packed"][:, 837].max()) == 0                 # plane 109 stays empty, as in the reference server's input
     rows = np.zeros((len(post), 1929), dtype=np.float16)
     rows[:, 0] = ((g["packed"].to(torch.int64).sum(dim=1) % 1009).to(torch.float16) / 1024).numpy()
     rows[:, 1] = g["black"].numpy()
