@@ -15,9 +15,10 @@ Small repeatable programs for a profiler capture (`-k regex:<kernel>`); they pri
     python bench.py --case gemm <kind> <M> <N> <K> <out> [act] [residual]
         one linear layer through `crl_linear` (kind: 0 f16, 1 e4m3, 2 int8 operands; out: 0 f16, 1 f32, 2 e4m3):
         three launches, then 20 more timed with CUDA events
-    python bench.py --case forward <f16|f8|i8> <positions> [chunk]
+    python bench.py --case forward <f16|f8|i8> <positions> [chunk [fuse_layernorm [precision]]]
         the BT4-shaped forward pass: plain timing of three passes, then one pass with the library's per-launch
-        CUDA events, grouped by kernel and shape
+        CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm 1 = LayerNorms as separate
+        passes; precision = CRL_PREC_* bit mask)
 """
 import argparse
 import json
@@ -208,6 +209,69 @@ def cpu_reference_forward(wl, sample, steps, warmup):
     return sum(times) / len(times), cores
 
 
+def cpu_baseline_and_accuracy(wl, sd, value_only, pos, engine_rows, sample=64, steps=4):
+    """The CPU-baseline leg: the fp32 oracle with the ENGINE'S weights runs the first sample * steps of the timed
+    positions in `steps` timed steps on all host threads (positions/s = the CPU baseline), and its outputs then
+    check the timed configuration's accuracy outside any timed region: top-1 over the legal moves, largest logit and
+    WDL errors, for the engine and - quantised engines - for the quantised CPU reference of the same number format,
+    so that the format's own noise and the kernels' share of it can be told apart."""
+    import numpy as np
+    from oracle import bt4spec, quantspec
+    L, d, ff, H = wl["dims"]
+    cfg = bt4spec.SpecConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only)
+    spec = bt4spec.BT4Spec(cfg)
+    spec.load_state_dict(sd)
+    spec.eval()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = sample * steps
+    tokens = pos["planes112"][:n].float().view(n, 64, 112)
+    outs, times = [], []
+    with torch.no_grad():
+        spec.forward_all(tokens[:sample])                          # warm-up step
+        for i in range(steps):
+            t0 = time.perf_counter()
+            o = spec.forward_all(tokens[i * sample:(i + 1) * sample])
+            if "policy" in o:
+                torch.softmax(o["policy"], -1)
+            times.append(time.perf_counter() - t0)
+            outs.append(o)
+    ref = {k: torch.cat([o[k] for o in outs]) for k in outs[0]}
+    cpu = {"value": sample / (sum(times) / len(times)), "unit": "positions/s", "cores": cores, "kind": "port",
+           "sample": f"{sample} positions per step x {steps} steps (the first {n} positions of the timed batch), fp32 PyTorch "
+                     "restatement of the reference forward with the engine's weights"}
+    legal = torch.from_numpy(np.unpackbits(pos["legal1858"][:n].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool))
+    ref_wdl = torch.softmax(ref["wdl"], -1)
+
+    def measure(pol, wdl, against_pol, against_wdl):
+        m = {"wdl_max_err": (wdl - against_wdl).abs().max().item()}
+        if pol is not None:
+            m["top1_legal"], m["logit_max_err"] = quantspec.agreement(pol, against_pol, legal)
+            m["logit_rms_err"] = (pol - against_pol)[legal].pow(2).mean().sqrt().item()
+        return m
+
+    ref_pol = bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal) if "policy" in ref else None
+    acc = {"positions": n, "against": "fp32 CPU oracle (oracle/bt4spec.py), arg-max over the legal moves of each position"}
+    acc.update(measure(engine_rows.get("policy"), engine_rows["wdl"], ref_pol, ref_wdl))
+    if wl["dtype"] == "f16":
+        acc["bars"] = {"logit_max_err": 2e-2, "wdl_max_err": 1e-2}
+        acc["meets_bars"] = acc["wdl_max_err"] <= 1e-2 and acc.get("logit_max_err", 0.0) <= 2e-2
+    else:
+        fmt = "e4m3" if wl["dtype"] == "f8e4m3" else "int8"
+        qs = quantspec.QuantSpec(spec, fmt=fmt)
+        if fmt == "e4m3":
+            qs.calibrate(tokens)
+        q = qs.forward_all(tokens)
+        q_pol = bt4spec.apply_policy_mask(q["policy"], legal_bits=legal) if "policy" in q else None
+        q_wdl = torch.softmax(q["wdl"], -1)
+        acc["quantised_reference_vs_fp32"] = measure(q_pol, q_wdl, ref_pol, ref_wdl)
+        acc["engine_vs_quantised_reference"] = measure(engine_rows.get("policy"), engine_rows["wdl"], q_pol, q_wdl)
+        acc["quantised_reference"] = f"oracle/quantspec.py, {fmt}: the same operands rounded at the same places in fp32 PyTorch"
+        acc["bars"] = {"top1_legal": 0.99, "wdl_max_err": 3e-2}
+        acc["meets_bars"] = acc["wdl_max_err"] <= 3e-2 and acc.get("top1_legal", 1.0) >= 0.99
+    return cpu, acc
+
+
 def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
     from chessrl_b200 import _lib
     lib = _lib.load()
@@ -246,13 +310,14 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
     return 0 if rc == 0 and status[0].item() == 0 else 1
 
 
-def forward_case(which, B, chunk=0):
+def forward_case(which, B, chunk=0, fuse_layernorm=0, precision=0):
     import collections
     import chessrl_b200 as crl
     from chessrl_b200 import synth
     from chessrl_b200.modules import _param_shapes
     dtype = {"f16": crl.DTYPE_F16, "f8": crl.DTYPE_F8E4M3, "i8": crl.DTYPE_I8}[which]
-    cfg = crl.EngineConfig.baseline(15, 1024, 1536, 32, smolgen=True, dtype=dtype, chunk=chunk)
+    cfg = crl.EngineConfig.baseline(15, 1024, 1536, 32, smolgen=True, dtype=dtype, chunk=chunk,
+                                    fuse_layernorm=fuse_layernorm, precision=precision)
     eng = crl.Engine(cfg, 0)
     eng.load_state_dict(synth.seeded_state_dict(_param_shapes(cfg), seed=0))
     planes = synth.synthetic_planes(B, 112, seed=1).cuda()
@@ -302,7 +367,7 @@ def main():
         if argv[0] == "gemm" and len(argv) >= 6:
             return gemm_case(*[int(x) for x in argv[1:8]])
         if argv[0] == "forward" and len(argv) >= 3:
-            return forward_case(argv[1], int(argv[2]), int(argv[3]) if len(argv) > 3 else 0)
+            return forward_case(argv[1], *[int(x) for x in argv[2:6]])
         print(__doc__)
         return 2
     ap = argparse.ArgumentParser()
@@ -364,7 +429,8 @@ def main():
     dtype = DTYPES[wl["dtype"]]
     cfg = crl.EngineConfig.baseline(L, d, ff, H, smolgen=wl["smolgen"], value_only=value_only, dtype=dtype, chunk=args.chunk)
     eng = crl.Engine(cfg, local_rank)
-    eng.load_state_dict(synth.seeded_state_dict(_param_shapes(cfg), seed=0))
+    weights = synth.seeded_state_dict(_param_shapes(cfg), seed=0)
+    eng.load_state_dict(weights)
     # seeded random playouts of 0..80 plies from the start position (the workload's stated input distribution):
     # 112-plane history encoding + legal-move bitsets from the library's own move generator
     from chessrl_b200 import positions
@@ -461,9 +527,9 @@ def main():
         peak, peak_note = peaks["bf16_tflops"], f"bf16_tflops, {peak_kind}"
     gm = prof["gemm"]
     achieved = top[2] / (top[1] * 1e-3) / 1e12 if top[1] > 0 else 0.0
-    # DRAM bytes per launch from the ncu capture of this kernel and shape (profiles/): 137.6 MB read + 355.5 MB
-    # written at M = 131072, N = 3072, K = 1024, e4m3 in and out (47 MB of the 402.7 MB output were still in L2 when
-    # the kernel ended); A and C scale with M
+    # DRAM bytes per launch from a profiler capture of this kernel and shape: 137.6 MB read + 355.5 MB written at
+    # M = 131072, N = 3072, K = 1024, e4m3 in and out (47 MB of the 402.7 MB output were still in L2 when the kernel
+    # ended); A and C grow in proportion to M, so the figure is scaled by the rows of the timed launch
     traffic = None
     if top_shape[1:] == (3072, 1024, 1):
         traffic = int(493.1e6 * top_shape[0] / 131072)
@@ -477,6 +543,13 @@ def main():
                 "peak_source": peak_note, "launches": gm["launches"], "ms_per_step": gm["ms"],
                 "share_of_step": gm["ms"] / sum(v["ms"] for v in prof.values()) if gm["ms"] else None,
                 "whole_forward_frac": value * fpp / 1e12 / world / peak if peak else None,
+                # the same fractions against driver-measured denominators: twice the bf16 figures of MEASURED_PEAKS.json
+                # (nominal FP8 : BF16 ratio) for FP8 / INT8, the bf16 figures themselves for FP16
+                "frac_vs_2x_bf16_burst": achieved / ((1.0 if dtype == crl.DTYPE_F16 else 2.0) * peaks["bf16_tflops"]),
+                "frac_vs_2x_bf16_sustained": achieved / ((1.0 if dtype == crl.DTYPE_F16 else 2.0) * peaks["bf16_tflops_sustained"]),
+                "whole_forward_frac_vs_2x_bf16_burst": value * fpp / 1e12 / world / ((1.0 if dtype == crl.DTYPE_F16 else 2.0) * peaks["bf16_tflops"]),
+                "whole_forward_frac_vs_2x_bf16_sustained": value * fpp / 1e12 / world / ((1.0 if dtype == crl.DTYPE_F16 else 2.0) * peaks["bf16_tflops_sustained"]),
+                "peaks_file": peak_kind,
                 "other_kernels": {k: {"ms": v["ms"], "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] else None,
                                       "launches": v["launches"]} for k, v in prof.items() if k != "gemm"},
                 "hbm_peak_gbs": peaks["hbm_gbs"]}
@@ -510,12 +583,14 @@ def main():
                    "f16": latency_b256(crl, synth, _param_shapes, wl["dims"], wl["smolgen"], crl.DTYPE_F16, dev),
                    "f8e4m3": latency_b256(crl, synth, _param_shapes, wl["dims"], wl["smolgen"], crl.DTYPE_F8E4M3, dev)}
 
-    cpu = None
+    cpu, accuracy = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample = 64 if d >= 1024 else 256
-        sec, cores = cpu_reference_forward(wl, sample, 2, 1)
-        cpu = {"value": sample / sec, "unit": "positions/s", "cores": cores, "kind": "port",
-               "sample": f"{sample} positions per step x 2 steps, fp32 PyTorch restatement of the reference forward"}
+        n_acc = min(256, per_rank)
+        rows = eng.forward(planes[:n_acc], layout=layout, legal_mask=None if value_only else bits[:n_acc])
+        torch.cuda.synchronize()
+        rows = {k: v.float().cpu() for k, v in rows.items()}
+        sample = min(64 if d >= 1024 else 256, n_acc)
+        cpu, accuracy = cpu_baseline_and_accuracy(wl, weights, value_only, pos, rows, sample=sample, steps=max(1, n_acc // sample))
 
     if rank == 0:
         print(json.dumps({
@@ -523,7 +598,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic (seeded random-playout positions, random-init weights)",
             "config": config, "e2e": e2e, "e2e_moves_only": e2e_moves,
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "accuracy": accuracy,
             "latency_b256": latency, "batch_sweep_positions_per_s": sweep,
             "device_status": st}))
     if dist is not None:

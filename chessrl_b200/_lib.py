@@ -7,7 +7,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libchessrl_b200.so")
+# CHESSRL_B200_LIB names another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("CHESSRL_B200_LIB") or os.path.join(HERE, "libchessrl_b200.so")
 
 # enums of include/chessrl_b200.h
 LN_POST, LN_PRE = 0, 1
@@ -22,6 +23,8 @@ PACKED104_BYTES = 840
 MASK_NONE, MASK_BITS, MASK_ADDITIVE, MASK_FROM_RECORDS = 0, 1, 2, 3
 OUT_F32, OUT_F16 = 0, 1
 VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
+FUSE_LN_AUTO, FUSE_LN_OFF = 0, 1
+PREC_QKV_F16, PREC_LN_F32, PREC_MISH_F32, PREC_ATTN_F32, PREC_FFN_F16, PREC_ATTN_GEMM_F16 = 1, 2, 4, 8, 16, 32
 
 EXPORTS = [
     "crl_create", "crl_destroy", "crl_set_weight", "crl_num_required_keys", "crl_required_key", "crl_finalize",
@@ -36,7 +39,7 @@ class Config(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "planes", "d_model", "n_layers", "n_heads", "d_ff", "ln_mode", "act", "ffn_act_pos", "bias_mode",
         "policy_mode", "value_mode", "dtype", "smolgen_compress", "smolgen_hidden", "smolgen_gen", "chunk", "pos_embed",
-        "lm_vocab")]
+        "lm_vocab", "fuse_layernorm", "precision")]
 
 
 class IO(ctypes.Structure):
@@ -67,6 +70,8 @@ class LinearArgs(ctypes.Structure):
         ("alpha", ctypes.c_float), ("act", ctypes.c_int32), ("out_scale", ctypes.c_float),
         ("row_scale", ctypes.c_void_p), ("col_scale", ctypes.c_void_p),
         ("device_status", ctypes.c_void_p), ("stream", ctypes.c_void_p),
+        ("ln_y", ctypes.c_void_p), ("ln_weight", ctypes.c_void_p), ("ln_bias", ctypes.c_void_p),
+        ("ln_x", ctypes.c_void_p), ("ln_x8", ctypes.c_void_p), ("ln_out8_scale", ctypes.c_float),
     ]
 
 

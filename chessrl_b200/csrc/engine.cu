@@ -29,6 +29,7 @@ struct LayerW {
   __half *wqkv = nullptr, *pos = nullptr, *u = nullptr, *v = nullptr, *wo = nullptr, *wff1 = nullptr, *wff2 = nullptr;
   float *bqkv = nullptr, *bo = nullptr, *bff1 = nullptr, *bff2 = nullptr;
   float *ln1w = nullptr, *ln1b = nullptr, *ln2w = nullptr, *ln2b = nullptr;
+  __half *ln1w16 = nullptr, *ln1b16 = nullptr, *ln2w16 = nullptr, *ln2b16 = nullptr;   // f16 copies for the GEMM-fused LayerNorm
   __half *sg_wc = nullptr, *sg_w1 = nullptr, *sg_w2 = nullptr;
   float *sg_b1 = nullptr, *sg_b2 = nullptr, *sg_ln1w = nullptr, *sg_ln1b = nullptr, *sg_ln2w = nullptr, *sg_ln2b = nullptr;
   // FP8: e4m3 weights, the multipliers they were quantised with, and the activation multipliers
@@ -37,7 +38,7 @@ struct LayerW {
   // INT8: per-output-channel symmetric weights and their scales
   int8_t *wqkv_q = nullptr, *wo_q = nullptr, *wff1_q = nullptr, *wff2_q = nullptr;
   float *cs_qkv = nullptr, *cs_o = nullptr, *cs_ff1 = nullptr, *cs_ff2 = nullptr;
-  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1, sa_qkv = 1;
+  float sa_in = 1, sa_ctx = 1, sa_ffn = 1, sa_hid = 1, sa_bias = 1, sa_qkv = 1, sa_gen = 1;
   // FP8: biases corrected for the mean effect of the weights' e4m3 rounding (filled by crl_calibrate)
   float *bqkv8 = nullptr, *bo8 = nullptr, *bff1_8 = nullptr, *bff2_8 = nullptr;
 };
@@ -68,7 +69,7 @@ struct crl_handle {
   float* mean_dev = nullptr;          // [L][4][max(d, ff)] column sums of the four GEMM inputs over the calibration batch
   float* mean_part = nullptr;         // [64][max(d, ff)] scratch of the column-sum kernel
   long long mean_rows = 0;            // rows summed so far in this calibration call
-  unsigned int* amax_dev = nullptr;   // [L*8] float bit patterns (5 taps per layer used)
+  unsigned int* amax_dev = nullptr;   // [L*8] float bit patterns (7 taps per layer used)
   int64_t launches = 0;
   // optional per-kernel timing (crl_profile): event pairs around every launch, by category
   struct ProfRec { cudaEvent_t a, b; int cat; double flops, bytes; int m, n, k, kind; };
@@ -77,6 +78,8 @@ struct crl_handle {
   bool profiling = false;
 
   __half *w_embed = nullptr, *pe16 = nullptr, *sg_shared = nullptr, *w_pt = nullptr, *w_qk = nullptr, *w_ph = nullptr;
+  uint8_t* sg_shared8 = nullptr;      // FP8 engine: e4m3 copy of the shared smolgen weight and its multiplier
+  float sw_shared = 1.0f;
   float *b_embed = nullptr, *lnE_w = nullptr, *lnE_b = nullptr, *gate_ea = nullptr, *gate_b = nullptr;
   float *lnF_w = nullptr, *lnF_b = nullptr, *b_pt = nullptr, *b_qk = nullptr;
   short* gather_idx = nullptr;
@@ -243,6 +246,7 @@ struct Workspace {
   uint8_t *x8, *t2_8, *t1_8;
   float *xs, *t2s, *t1s;   // INT8: per-token scales of x8 / t2_8 / t1_8
   __half *sg_c, *sg_h1, *sg_h1n, *sg_h2, *sg_h2n, *sg_bias;
+  uint8_t* sg_h2n8;   // FP8 engine: e4m3 copy of the normalised generator rows (A operand of the bias GEMM)
   __half *flat;     // [bc, 4096] policy scores (dense form)
   float* logits;    // [bc, 1929] f32 (dense form)
   __half *v2, *v2q;
@@ -287,6 +291,7 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc, int64_t total) {
   w.sg_h1n = reinterpret_cast<__half*>(take(sg ? bc * c.smolgen_hidden * 2 : 0));
   w.sg_h2 = reinterpret_cast<__half*>(take(sg ? bc * hg * 2 : 0));
   w.sg_h2n = reinterpret_cast<__half*>(take(sg ? bc * hg * 2 : 0));
+  w.sg_h2n8 = reinterpret_cast<uint8_t*>(take(sg && c.dtype == CRL_DTYPE_F8E4M3 ? bc * hg : 0));
   w.sg_bias = reinterpret_cast<__half*>(take(sg ? static_cast<size_t>(bc) * c.n_heads * 4096 * 2 : 0));
   const bool dense = c.policy_mode == CRL_POLICY_DENSE4096;
   const bool lm = c.policy_mode == CRL_POLICY_LM_HEAD;
@@ -329,6 +334,10 @@ struct Lin {
   const __half* res = nullptr; long long ldr = 0; int res_mod = 0;
   float alpha = 1.0f; int act = kActNone; float out_scale = 1.0f;
   const float* row_scale = nullptr; const float* col_scale = nullptr;
+  // fused LayerNorm: A = LN(ln_y) * w + b, normalised inside the GEMM kernel, written to ln_x (f16) / ln_x8 (e4m3)
+  const __half* ln_y = nullptr; const __half* ln_w16 = nullptr; const __half* ln_b16 = nullptr;
+  __half* ln_x = nullptr; uint8_t* ln_x8 = nullptr; float ln_out8_scale = 1.0f;
+  int precise_act = 0;
 };
 
 int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
@@ -340,6 +349,8 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.bias = l.bias; g.p.residual = l.res; g.p.ldr = l.ldr; g.p.res_mod = l.res_mod;
   g.p.alpha = l.alpha; g.p.row_scale = l.row_scale; g.p.col_scale = l.col_scale;
   g.p.act = l.act; g.p.out_scale = l.out_scale; g.p.status = h->status_dev;
+  g.p.ln_y = l.ln_y; g.p.ln_ldy = l.k; g.p.ln_w16 = l.ln_w16; g.p.ln_b16 = l.ln_b16; g.p.ln_x = l.ln_x; g.p.ln_x8 = l.ln_x8;
+  g.p.ln_out8_scale = l.ln_out8_scale; g.p.precise_act = l.precise_act;
   const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
                static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
@@ -362,7 +373,7 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
   p.yq = yq; p.yq_scale = yq_scale;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * d * (2 + (y != nullptr ? 2 : 0) + (y8 != nullptr ? 1 : 0)));
-  if (yq == nullptr && gate_ea == nullptr && rows >= 8192) {
+  if (yq == nullptr && gate_ea == nullptr && rows >= 8192 && (h->cfg.precision & CRL_PREC_LN_F32) == 0) {
     const long long want = (rows + 7) / 8;
     const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 2));
     ln_rows_persistent_kernel<<<grid, 256, 0, s>>>(p);
@@ -484,10 +495,21 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   const long long M = bc * 64;
   const bool f8 = c.dtype == CRL_DTYPE_F8E4M3 && !calib;
   const bool i8 = c.dtype == CRL_DTYPE_I8;
+  const int prec = c.precision;
+  const bool attn_f32 = (prec & CRL_PREC_ATTN_F32) != 0;
+  const bool f8_attn = f8 && (prec & CRL_PREC_ATTN_GEMM_F16) == 0;   // QKV / out-projection on e4m3 operands
+  const bool f8_ffn = f8 && (prec & CRL_PREC_FFN_F16) == 0;          // ff1 / ff2 on e4m3 operands
   // FP8 engine on the TMA attention path: the QKV projection writes e4m3 and attention reads it
-  const bool qkv8 = f8 && h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN);
+  const bool qkv8 = f8 && h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN) &&
+                    (prec & (CRL_PREC_QKV_F16 | CRL_PREC_ATTN_F32 | CRL_PREC_ATTN_GEMM_F16)) == 0;
+  const bool ctx8 = f8_attn;      // attention writes its context as e4m3 for an e4m3 out-projection
   int8_t* const xq = reinterpret_cast<int8_t*>(w.x8);
   const int act = act_of(c);
+  // Post-LN blocks on large passes: the LayerNorm in front of ff1 and the one in front of the next block's QKV
+  // projection run inside those GEMM kernels (their own warps normalise a row block ahead of the MMAs) instead of
+  // as separate passes over the rows.
+  const bool fuse_ln = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm != CRL_FUSE_LN_OFF &&
+                       (prec & CRL_PREC_LN_F32) == 0 && gemm_can_fuse_ln(M, std::min(3 * d, ff), d, h->num_sms);
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
   {
@@ -541,11 +563,16 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     // QKV projection (attn.py:501-503 fused into one [3d, d] weight)
     {
       Lin q; q.m = M; q.n = 3 * d; q.k = d; q.c = w.t1; q.ldc = 3 * d; q.bias = L.bqkv;
-      if (f8) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); q.bias = L.bqkv8; }
+      if (f8_attn) { q.kind = kKindF8; q.a = attn_in8; q.w = L.wqkv8; q.alpha = 1.0f / (L.sa_in * L.sw_qkv); q.bias = L.bqkv8; }
+      else if (!i8) { q.a = attn_in; q.w = L.wqkv; }
       if (qkv8) { q.out = kOutE4M3; q.out_scale = L.sa_qkv; }   // Q, K, V cross HBM as e4m3 (one scale for the three)
       else if (i8) { q.kind = kKindI8; q.a = w.x8; q.w = L.wqkv_q; q.row_scale = w.xs; q.col_scale = L.cs_qkv; }
-      else { q.a = attn_in; q.w = L.wqkv; }
       q.lda = d; q.ldw = d;
+      if (fuse_ln && l > 0) {      // norm2 of the previous block: w.y -> w.x (+ w.x8), inside this kernel
+        const LayerW& P = h->layers[l - 1];
+        q.ln_y = w.y; q.ln_w16 = P.ln2w16; q.ln_b16 = P.ln2b16; q.ln_x = w.x; q.ln_x8 = f8 ? w.x8 : nullptr; q.ln_out8_scale = L.sa_in;
+        // (the e4m3 copy is written even when this GEMM reads the f16 rows: the smolgen compression reads it)
+      }
       if ((rc = linear(h, q, s)) != CRL_OK) return rc;
       if (calib && (rc = tap_amax(h, w.t1, M, 3 * d, l * 8 + 5, s)) != CRL_OK) return rc;
     }
@@ -562,10 +589,15 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       Lin e; e.a = w.sg_h1n; e.lda = hid; e.w = L.sg_w2; e.ldw = hid; e.c = w.sg_h2; e.ldc = H * gen; e.m = bc; e.n = H * gen;
       e.k = hid; e.bias = L.sg_b2; e.act = act;
       if ((rc = linear(h, e, s)) != CRL_OK) return rc;
-      if ((rc = layer_norm(h, w.sg_h2, bc * H, gen, L.sg_ln2w, L.sg_ln2b, w.sg_h2n, nullptr, 1.0f, nullptr, nullptr, s)) != CRL_OK) return rc;
+      // FP8 engine (default precision): the generator rows get an e4m3 copy and the 256 -> 4096 product runs on e4m3
+      // operands (it is bound by operand traffic, and its rounding is two orders of magnitude below the block GEMMs')
+      const bool bias8 = qkv8 && gen % 16 == 0;
+      if ((rc = layer_norm(h, w.sg_h2, bc * H, gen, L.sg_ln2w, L.sg_ln2b, w.sg_h2n, bias8 ? w.sg_h2n8 : nullptr, bias8 ? L.sa_gen : 1.0f, nullptr, nullptr, s)) != CRL_OK) return rc;
+      if (calib && (rc = tap_amax(h, w.sg_h2n, bc * H, gen, l * 8 + 6, s)) != CRL_OK) return rc;
       Lin f; f.a = w.sg_h2n; f.lda = gen; f.w = h->sg_shared; f.ldw = gen; f.c = w.sg_bias; f.ldc = 4096; f.m = bc * H; f.n = 4096;
       f.k = gen;
-      if (f8) { f.out = kOutE4M3; f.out_scale = L.sa_bias; }   // the bias tile crosses HBM as e4m3
+      if (bias8) { f.kind = kKindF8; f.a = w.sg_h2n8; f.w = h->sg_shared8; f.alpha = 1.0f / (L.sa_gen * h->sw_shared); }
+      if (qkv8) { f.out = kOutE4M3; f.out_scale = L.sa_bias; }   // the bias tile crosses HBM as e4m3
       if ((rc = linear(h, f, s)) != CRL_OK) return rc;
       if (calib && (rc = tap_amax(h, w.sg_bias, bc * H, 4096, l * 8 + 4, s)) != CRL_OK) return rc;
     }
@@ -576,11 +608,11 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       a.bias = w.sg_bias; a.pos = L.pos; a.u = L.u; a.v = L.v;
       a.scale = c.bias_mode == CRL_BIAS_RELPOS ? 1.0f / std::sqrt(static_cast<float>(d)) : 1.0f / std::sqrt(static_cast<float>(h->hd));
       a.ldo = d;
-      if (f8) { a.out = nullptr; a.out8 = w.t2_8; a.out8_scale = L.sa_ctx; }
+      if (ctx8) { a.out = nullptr; a.out8 = w.t2_8; a.out8_scale = L.sa_ctx; }
       else { a.out = w.t2; a.out8 = nullptr; a.out8_scale = 1.0f; }
       ProfScope ps(h, s, kCatAttention, 4.0 * M * 64 * d,
-                   static_cast<double>(M) * d * (qkv8 ? 1 : 2) * 3 + static_cast<double>(M) * d * (f8 ? 1 : 2) +
-                       (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * (f8 ? 4096 : 8192) : 0.0));
+                   static_cast<double>(M) * d * (qkv8 ? 1 : 2) * 3 + static_cast<double>(M) * d * (ctx8 ? 1 : 2) +
+                       (c.bias_mode == CRL_BIAS_SMOLGEN ? static_cast<double>(bc) * H * (qkv8 ? 4096 : 8192) : 0.0));
       if (qkv8) {
         AttnTma8Params t{};
         t.B = static_cast<int>(bc); t.H = H; t.scale = a.scale; t.d = d; t.status = h->status_dev;
@@ -589,13 +621,13 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
         t.bias_mult = 1.0f / L.sa_bias;
         t.out_mult = L.sa_ctx / L.sa_qkv;
         if ((rc = attention_tma8_launch(h, t, reinterpret_cast<const uint8_t*>(w.t1), w.sg_bias, w.t2_8, s)) != CRL_OK) return rc;
-      } else if (h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN)) {
+      } else if (!attn_f32 && h->hd == 32 && (c.bias_mode == CRL_BIAS_NONE || c.bias_mode == CRL_BIAS_SMOLGEN)) {
         AttnTmaParams t{};
         t.B = static_cast<int>(bc); t.H = H; t.scale = a.scale; t.d = d; t.status = h->status_dev;
-        t.has_bias = c.bias_mode == CRL_BIAS_SMOLGEN ? (f8 ? 2 : 1) : 0;
-        t.bias_mult = f8 ? 1.0f / L.sa_bias : 1.0f;
-        t.out_e4m3 = f8 ? 1 : 0; t.out_scale = f8 ? L.sa_ctx : 1.0f;
-        if ((rc = attention_tma_launch(h, t, w.t1, w.sg_bias, f8 ? static_cast<void*>(w.t2_8) : static_cast<void*>(w.t2), s)) != CRL_OK)
+        t.has_bias = c.bias_mode == CRL_BIAS_SMOLGEN ? 1 : 0;      // f16 bias tile (the e4m3 tile goes with e4m3 Q/K/V)
+        t.bias_mult = 1.0f;
+        t.out_e4m3 = ctx8 ? 1 : 0; t.out_scale = ctx8 ? L.sa_ctx : 1.0f;
+        if ((rc = attention_tma_launch(h, t, w.t1, w.sg_bias, ctx8 ? static_cast<void*>(w.t2_8) : static_cast<void*>(w.t2), s)) != CRL_OK)
           return rc;
       } else {
         CRL_CUDA(h, attention_launch(a, h->hd, c.bias_mode, s));
@@ -609,14 +641,15 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     {
       Lin o; o.m = M; o.n = d; o.k = d; o.bias = L.bo; o.res = w.x; o.ldr = d; o.lda = d; o.ldw = d;
       o.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; o.ldc = d;
-      if (f8) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); o.bias = L.bo8; }
+      if (f8_attn) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); o.bias = L.bo8; }
       else if (i8) { o.kind = kKindI8; o.a = w.t2_8; o.w = L.wo_q; o.row_scale = w.t2s; o.col_scale = L.cs_o; }
       else { o.a = w.t2; o.w = L.wo; }
       if ((rc = linear(h, o, s)) != CRL_OK) return rc;
     }
     const __half* ffn_in;
     if (c.ln_mode == CRL_LN_POST) {
-      if ((rc = layer_norm(h, w.y, M, d, L.ln1w, L.ln1b, w.x, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
+      if (!fuse_ln &&
+          (rc = layer_norm(h, w.y, M, d, L.ln1w, L.ln1b, w.x, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
       ffn_in = w.x;
     } else {
       if ((rc = layer_norm(h, w.x, M, d, L.ln2w, L.ln2b, w.xn, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
@@ -628,9 +661,13 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
     {
       Lin a; a.m = M; a.n = ff; a.k = d; a.bias = L.bff1; a.lda = d; a.ldw = d; a.ldc = ff;
       a.act = c.ffn_act_pos == CRL_FFN_ACT_MID ? act : kActNone;
-      if (f8) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; a.bias = L.bff1_8; }
+      a.precise_act = (prec & CRL_PREC_MISH_F32) != 0;
+      if (f8_ffn) { a.kind = kKindF8; a.a = w.x8; a.w = L.wff1_8; a.alpha = 1.0f / (L.sa_ffn * L.sw_ff1); a.c = w.t1_8; a.out = kOutE4M3; a.out_scale = L.sa_hid; a.bias = L.bff1_8; }
       else if (i8) { a.kind = kKindI8; a.a = w.x8; a.w = L.wff1_q; a.row_scale = w.xs; a.col_scale = L.cs_ff1; a.c = w.t1; }
       else { a.a = ffn_in; a.w = L.wff1; a.c = w.t1; }
+      if (fuse_ln) {               // norm1 of this block: w.y -> w.x (+ w.x8), inside this kernel
+        a.ln_y = w.y; a.ln_w16 = L.ln1w16; a.ln_b16 = L.ln1b16; a.ln_x = w.x; a.ln_x8 = f8 ? w.x8 : nullptr; a.ln_out8_scale = L.sa_ffn;
+      }
       if ((rc = linear(h, a, s)) != CRL_OK) return rc;
       if (i8 && (rc = quant_rows_i8(h, w.t1, M, ff, w.t1_8, w.t1s, s)) != CRL_OK) return rc;
       if (calib && (rc = tap_amax(h, w.t1, M, ff, l * 8 + 3, s)) != CRL_OK) return rc;
@@ -638,12 +675,12 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       Lin b; b.m = M; b.n = d; b.k = ff; b.bias = L.bff2; b.lda = ff; b.ldw = ff; b.res = w.x; b.ldr = d;
       b.act = c.ffn_act_pos == CRL_FFN_ACT_END ? act : kActNone;
       b.c = c.ln_mode == CRL_LN_POST ? w.y : w.x; b.ldc = d;
-      if (f8) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); b.bias = L.bff2_8; }
+      if (f8_ffn) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); b.bias = L.bff2_8; }
       else if (i8) { b.kind = kKindI8; b.a = w.t1_8; b.w = L.wff2_q; b.row_scale = w.t1s; b.col_scale = L.cs_ff2; }
       else { b.a = w.t1; b.w = L.wff2; }
       if ((rc = linear(h, b, s)) != CRL_OK) return rc;
     }
-    if (c.ln_mode == CRL_LN_POST) {
+    if (c.ln_mode == CRL_LN_POST && !(fuse_ln && l + 1 < c.n_layers)) {
       const bool emit8 = f8 && l + 1 < c.n_layers;
       if ((rc = layer_norm(h, w.y, M, d, L.ln2w, L.ln2b, w.x, emit8 ? w.x8 : nullptr,
                            emit8 ? h->layers[l + 1].sa_in : 1.0f, nullptr, nullptr, s,
@@ -897,6 +934,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
       c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
   if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3 && c.dtype != CRL_DTYPE_I8) return CRL_ERR_UNSUPPORTED;
+  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_OFF || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
   if (c.dtype == CRL_DTYPE_I8 && (c.d_model % 16 != 0 || c.d_ff % 16 != 0)) return CRL_ERR_SHAPE;
   if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&
@@ -1075,6 +1113,8 @@ int crl_finalize(crl_handle* h) {
     UP32(L.bo, lkey(l, "attention.out_proj.bias"), d);
     UP32(L.ln1w, lkey(l, "norm1.weight"), d); UP32(L.ln1b, lkey(l, "norm1.bias"), d);
     UP32(L.ln2w, lkey(l, "norm2.weight"), d); UP32(L.ln2b, lkey(l, "norm2.bias"), d);
+    UP16(L.ln1w16, lkey(l, "norm1.weight"), 1, d, d); UP16(L.ln1b16, lkey(l, "norm1.bias"), 1, d, d);
+    UP16(L.ln2w16, lkey(l, "norm2.weight"), 1, d, d); UP16(L.ln2b16, lkey(l, "norm2.bias"), 1, d, d);
     UP16(L.wff1, lkey(l, "ff1.weight"), ff, d, d); UP32(L.bff1, lkey(l, "ff1.bias"), ff);
     UP16(L.wff2, lkey(l, "ff2.weight"), d, ff, ff); UP32(L.bff2, lkey(l, "ff2.bias"), d);
     if (c.bias_mode == CRL_BIAS_RELPOS) {
@@ -1124,6 +1164,10 @@ int crl_finalize(crl_handle* h) {
     }
   }
   if (c.bias_mode == CRL_BIAS_SMOLGEN) UP16(h->sg_shared, "smolgen_shared.weight", 4096, c.smolgen_gen, c.smolgen_gen);
+  if (c.bias_mode == CRL_BIAS_SMOLGEN && c.dtype == CRL_DTYPE_F8E4M3) {
+    const auto& ws = *get(h, "smolgen_shared.weight");
+    if ((rc = upload_e4m3(h, &h->sg_shared8, &h->sw_shared, ws.data(), ws.size())) != CRL_OK) return rc;
+  }
   if (c.ln_mode == CRL_LN_PRE) { UP32(h->lnF_w, "norm_f.weight", d); UP32(h->lnF_b, "norm_f.bias", d); }
   if (c.policy_mode == CRL_POLICY_LM_HEAD) UP16(h->w_ph, "lm_head.weight", c.lm_vocab, d, d);
   if (c.policy_mode == CRL_POLICY_DENSE4096 || c.policy_mode == CRL_POLICY_GATHER1858) {
@@ -1224,6 +1268,7 @@ int crl_calibrate(crl_handle* h, const void* planes, int32_t layout, int64_t bat
     h->layers[l].sa_hid = mult(amax[l * 8 + 3]);
     h->layers[l].sa_bias = mult(amax[l * 8 + 4]);
     h->layers[l].sa_qkv = mult(amax[l * 8 + 5]);
+    h->layers[l].sa_gen = mult(amax[l * 8 + 6]);
   }
   if (correct && (rc = correct_fp8_biases(h, batch * 64, s)) != CRL_OK) return rc;
   h->calibrated = true;
@@ -1393,6 +1438,13 @@ int crl_linear_ex(const crl_linear_args* x) {
   g.p.alpha = x->alpha; g.p.row_scale = x->row_scale; g.p.col_scale = x->col_scale; g.p.act = x->act;
   g.p.out_scale = x->out_dtype == kOutE4M3 ? x->out_scale : 1.0f;
   g.p.status = x->device_status;
+  if (x->ln_y != nullptr) {
+    if (x->ln_weight == nullptr || x->ln_bias == nullptr) return CRL_ERR_INVALID;
+    g.p.ln_y = static_cast<const __half*>(x->ln_y); g.p.ln_ldy = x->k;
+    g.p.ln_w16 = static_cast<const __half*>(x->ln_weight); g.p.ln_b16 = static_cast<const __half*>(x->ln_bias);
+    g.p.ln_x = static_cast<__half*>(x->ln_x); g.p.ln_x8 = static_cast<uint8_t*>(x->ln_x8); g.p.ln_out8_scale = x->ln_out8_scale;
+    if (x->a != (x->kind == CRL_DTYPE_F16 ? x->ln_x : x->ln_x8) || x->lda != x->k) return CRL_ERR_INVALID;
+  }
   return gemm_launch(g, sms, static_cast<cudaStream_t>(x->stream));
 }
 

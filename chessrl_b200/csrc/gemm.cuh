@@ -40,8 +40,22 @@ struct GemmParams {
   int* status;             // device status word
   int use_tma_store;       // host built a tensor map for C (f16 / e4m3 output, 16-byte aligned pitch)
   int use_tma_res;         // host built a tensor map for the residual (res_mod == 0, 16-byte aligned pitch)
+  // LNA kernels: A is LayerNorm(y) of these rows, produced inside the GEMM kernel by its own warps, a row block
+  // ahead of the MMAs (see ln_rows_of_block). x (f16) and x8 (e4m3 * out8_scale) are written to global memory; the
+  // tensor map of A points at whichever of the two the MMA kind consumes.
+  const __half* ln_y;      // [M, K] f16, row pitch ln_ldy
+  long long ln_ldy;
+  const __half* ln_w16;    // [K] f16 LayerNorm weight
+  const __half* ln_b16;    // [K] f16 LayerNorm bias
+  __half* ln_x;            // [M, K] f16 out (nullable), pitch K
+  uint8_t* ln_x8;          // [M, K] e4m3 out (nullable), pitch K
+  float ln_out8_scale;
+  int precise_act;         // 1: Mish into an e4m3 output in fp32 instead of on packed f16 pairs
 };
 
+#ifndef CRL_PAIR_O8_STAGES
+#define CRL_PAIR_O8_STAGES 5     // ring stages of the CTA-pair kernels with an e4m3 output (2 KB slabs leave room for 6)
+#endif
 constexpr int kGemmThreads = 576;   // TMA warp + MMA warp + 16 epilogue warps
 
 constexpr int kEpiWarps = 16;
@@ -54,8 +68,10 @@ constexpr int kEpiWarps = 16;
 //   O8  = 1: the output is e4m3 (2 KB slabs), 0: f16 (4 KB slabs);
 //   RES = 1 (f16 output only): the residual slab arrives by TMA in the warp's own slab buffer, requested a
 //         tile ahead, and the result overwrites it in place before the store.
-template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0>
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0>
 struct GemmCfg {
+  static_assert(!LNA || PAIR, "the fused LayerNorm exists for CTA pairs only");
+  static constexpr int THREADS = kGemmThreads;
   static_assert(!(RES && O8), "the residual variant writes f16");
   static_assert(!PAIR || BN == 256, "pairs work on 256 x 256 tiles");
   static constexpr int BM = 128;           // rows per CTA
@@ -71,14 +87,21 @@ struct GemmCfg {
   // per epilogue warp: pairs one slab (32 rows x 64 columns of the output type), single CTAs one 32 x 32 chunk
   static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : 4096) : 2048;
   // pairs: f16 slabs leave room for five 32 KB stages (four with the int8 scale table)
-  static constexpr int STAGES = PAIR ? ((!O8 && KIND == kKindI8) ? 4 : 5) : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
+  static constexpr int STAGES = PAIR ? ((!O8 && KIND == kKindI8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
+                                     : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
   // after the stages: the tables, the per-warp slabs (1024-byte aligned: TMA swizzles by absolute address
   // bits), then the mbarriers (ring, accumulators, one per epilogue warp for its residual slab) + TMEM slot
   static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr uint32_t BAR_OFF = EPI_OFF + TAB_BYTES + kEpiWarps * SLOT_BYTES;
-  static constexpr uint32_t USED_BYTES = BAR_OFF + 128 + kEpiWarps * 8;
-  static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + ((PAIR && !O8) ? 512 : 896) /*alignment slack*/;
+  // barrier region: [0,128) ring (2 x STAGES <= 12) and accumulator (4) mbarriers, [128,144) the TMEM address slot,
+  // [144, 144 + 8 x 16) one mbarrier per epilogue warp (residual slab), then the LayerNorm progress counter
+  static_assert(2 * STAGES + 4 <= 16, "the ring and accumulator barriers share 128 bytes");
+  static constexpr uint32_t TMEM_SLOT_OFF = BAR_OFF + 128;
+  static constexpr uint32_t RBAR_OFF = BAR_OFF + 144;
+  static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 8;
+  static constexpr uint32_t USED_BYTES = LN_COUNTER_OFF + 16;
+  static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + ((PAIR && (!O8 || STAGES > 5)) ? 496 : 896) /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
 };
 
@@ -133,11 +156,130 @@ __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off,
       static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-template <int BN, int KIND, int PAIR, int RES, int O8>
+// LayerNorm (eps 1e-5, affine) of rows [row0, row0 + nrows) of p.ln_y, shared among `nw` warps: warp `wi` owns rows
+// wi, wi + nw, ... and this call does its rows number j0 .. j0 + cnt - 1, with the next row's loads in flight while
+// one is normalised. Same arithmetic as
+// ln_rows_persistent_kernel (fp32 statistics, f16 affine), so a network gives the same bits whichever kernel
+// normalises a row. K <= 1024, K % 8 == 0.
+__device__ __forceinline__ void ln_rows_of_block(const GemmParams& p, long long row0, int nrows, int wi, int nw, int lane,
+                                                 int j0 = 0, int cnt = 1 << 20) {
+  constexpr int NV = 4;
+  const int d = p.K;
+  long long row = row0 + wi + (long long)j0 * nw;       // the warp's rows j0, j0 + 1, ... (of wi, wi + nw, ...)
+  long long end = (row0 + nrows < p.M) ? row0 + nrows : p.M;
+  if (cnt < (1 << 20)) {                                // at most cnt rows: the last one is row + (cnt - 1) * nw
+    const long long lim = row + (long long)(cnt - 1) * nw + 1;
+    if (lim < end) end = lim;
+  }
+  if (row >= end) return;
+  uint4 raw[NV], nxt[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    raw[i] = c < d ? *reinterpret_cast<const uint4*>(p.ln_y + row * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const __half2 s8 = __floats2half2_rn(p.ln_out8_scale, p.ln_out8_scale);
+  for (; row < end; row += nw) {
+    const long long nrow = row + nw;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      nxt[i] = (nrow < end && c < d) ? *reinterpret_cast<const uint4*>(p.ln_y + nrow * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float sum = 0.0f, sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        sum += f.x + f.y;
+        sq = fmaf(f.x, f.x, fmaf(f.y, f.y, sq));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    }
+    const float mean = sum / d;
+    const float rstd = rsqrtf(fmaxf(sq / d - mean * mean, 0.0f) + 1e-5f);
+    const float shift = -mean * rstd;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < d) {
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.ln_w16 + c));
+        const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.ln_b16 + c));
+        const __half2* wh = reinterpret_cast<const __half2*>(&w4);
+        const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+        uint32_t o16[4];
+        __half2 y2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
+          y2[j] = __hfma2(xn, wh[j], bh[j]);
+          o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
+        }
+        if (p.ln_x != nullptr) *reinterpret_cast<uint4*>(p.ln_x + row * p.K + c) = make_uint4(o16[0], o16[1], o16[2], o16[3]);
+        if (p.ln_x8 != nullptr) {
+          uint32_t w8[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+            w8[j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                    (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+          }
+          *reinterpret_cast<uint2*>(p.ln_x8 + row * p.K + c) = make_uint2(w8[0], w8[1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) raw[i] = nxt[i];
+  }
+}
+
+// Hint: bring the warp's rows number j0 .. j0 + cnt - 1 of a row block into L2 (one bulk prefetch per row, issued
+// by lane j - j0), so that the loads of ln_rows_of_block find them there instead of paying an HBM round trip while
+// the accumulator of the next tile is waiting to be drained.
+__device__ __forceinline__ void ln_prefetch_rows(const GemmParams& p, long long row0, int nrows, int wi, int nw, int lane, int j0, int cnt) {
+  if (lane < cnt) {
+    const long long row = row0 + wi + (long long)(j0 + lane) * nw;
+    const long long end = (row0 + nrows < p.M) ? row0 + nrows : p.M;
+    if (row < end)
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ln_y + row * p.ln_ldy), "r"(uint32_t(p.K) * 2u) : "memory");
+  }
+}
+
+// A warp's rows of a row block are written: order them before the TMA loads that will read them (generic-proxy
+// stores, async-proxy loads of the same global memory), then count the warp in.
+__device__ __forceinline__ void ln_signal_block_done(uint32_t counter_smem, int lane) {
+  __threadfence();                                          // every lane's rows are in L2 ...
+  asm volatile("fence.proxy.async.global;" ::: "memory");   // ... and ordered before async-proxy reads of them
+  __syncwarp();
+  if (lane == 0) asm volatile("red.release.gpu.shared::cta.add.u32 [%0], 1;" ::"r"(counter_smem) : "memory");
+}
+// Bounded wait of the TMA producer for the counter to reach `target`.
+__device__ __forceinline__ bool ln_wait_blocks(uint32_t counter_smem, uint32_t target) {
+  for (int i = 0; i < (1 << 23); ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(counter_smem) : "memory");
+    if (v >= target) {
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      return true;
+    }
+    if (i > 2048) __nanosleep(64);
+  }
+  return false;
+}
+
+template <int BN, int KIND, int PAIR, int RES, int O8, int LNA>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
-  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8>;
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA>;
   constexpr int BM = Cfg::BM, TM = Cfg::TM, BK = Cfg::BK, STAGES = Cfg::STAGES;
   // cluster rank (0 = leader) and the persistent worker this CTA belongs to
   const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
@@ -154,7 +296,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_slot =
-      reinterpret_cast<uint32_t*>(smem + Cfg::BAR_OFF + 8 * (2 * STAGES + 4));
+      reinterpret_cast<uint32_t*>(smem + Cfg::TMEM_SLOT_OFF);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -167,6 +309,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
+  // The i-th tile of this worker. Plain kernels deal the tiles out round-robin (n fastest); LNA kernels give a
+  // worker whole row blocks (all column tiles of row block worker, worker + W, ...), because the worker's own
+  // warps normalise the rows of a block before its first tile loads them.
+  auto tile_of = [&](int i, int& mi, int& ni) -> bool {
+    if constexpr (LNA) {
+      mi = worker + (i / tiles_n) * num_workers;
+      ni = i % tiles_n;
+      return mi < tiles_m;
+    } else {
+      const int t = worker + i * num_workers;
+      mi = t / tiles_n;
+      ni = t % tiles_n;
+      return t < num_tiles;
+    }
+  };
+  const uint32_t ln_counter = base + Cfg::LN_COUNTER_OFF;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -175,7 +333,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar0 + 128u + 8u * w, 1);
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(base + Cfg::RBAR_OFF + 8u * w, 1);
+    asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(ln_counter), "r"(0u) : "memory");
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
@@ -198,9 +357,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = worker; t < num_tiles && ok; t += num_workers) {
-        const int m0 = (t / tiles_n) * TM + rank * BM;                  // this CTA's rows of A
-        const int n0 = (t % tiles_n) * BN + rank * (PAIR ? BN / 2 : 0);  // this CTA's rows of W
+      int mi = 0, ni = 0;
+      for (int i = 0; ok && tile_of(i, mi, ni); ++i) {
+        const int m0 = mi * TM + rank * BM;                  // this CTA's rows of A
+        const int n0 = ni * BN + rank * (PAIR ? BN / 2 : 0);  // this CTA's rows of W
+        if constexpr (LNA) {
+          // the first tile of a row block waits until this CTA's 128 rows of it are normalised: every epilogue warp
+          // counts in once per block, and no warp starts on block j + 1 before block j's tiles run
+          if (ni == 0 && !ln_wait_blocks(ln_counter, uint32_t(kEpiWarps * (i / tiles_n + 1)))) {
+            atomicCAS(p.status, 0, kDevTimeoutProducer);
+            ok = false;
+            break;
+          }
+        }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
             atomicCAS(p.status, 0, kDevTimeoutProducer);
@@ -212,8 +381,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (PAIR) {
             // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
             const uint32_t lead_full = mapa_u32(full_bar(s), 0);
+#ifdef CRL_EXP_SKIP_A
+            const bool skip_a = LNA != 0 && ni > 0;     // timing experiment only: wrong results
+            if (rank == 0) mbar_expect_tx(full_bar(s), skip_a ? 2 * Cfg::B_BYTES : 2 * Cfg::STAGE_BYTES);
+            if (!skip_a) tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, lead_full);
+#else
             if (rank == 0) mbar_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
             tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, lead_full);
+#endif
             tma_load_2d_pair(b_dst, &tmB, kb * BK, n0, lead_full);
           } else {
             mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
@@ -234,7 +409,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0;
       int local = 0;
       bool ok = true;
-      for (int t = worker; t < num_tiles && ok; t += num_workers, ++local) {
+      int mi = 0, ni = 0;
+      for (; ok && tile_of(local, mi, ni); ++local) {
         const int as = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
         if (!mbar_wait(tempty_bar(as), aph ^ 1u)) {
@@ -275,34 +451,78 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     float* cs_s = bias_s + 2 * BN;                                                  // [2][BN] per-column scales (int8)
     if constexpr (PAIR) {
       // Slab epilogue. Per tile this warp owns rows [32*quarter, +32) x columns [64*part, +64) of the CTA's
-      // accumulator half, drained as four 16-column pieces with the TMEM load of the next piece in flight while
-      // one is worked on; the accumulator buffer goes back to the MMA warp as soon as the last piece sits in
-      // registers, and the finished slab leaves through one TMA store (64- or 128-byte rows). The slab buffer is
+      // accumulator half, drained in two TMEM loads of 32 columns; the accumulator buffer goes back to the MMA warp
+      // as soon as the second load has landed in registers, before the arithmetic on it, and the finished slab
+      // leaves through one TMA store (64- or 128-byte rows). The slab buffer is
       // free again long before the next tile needs it, so no store is ever waited for inside a tile.
       const uint32_t slot = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + ew * Cfg::SLOT_BYTES;
-      const uint32_t rbar = bar0 + 128u + 8u * ew;
+      const uint32_t rbar = base + Cfg::RBAR_OFF + 8u * ew;
       uint32_t rph = 0;
       bool res_pending = false;
       // RES: the residual slab (32 rows x 64 f16, 128-byte swizzle) is fetched into the slab buffer itself, a tile
       // ahead: right after this tile's store has read the buffer.
-      auto res_issue = [&](int tile) {
+      auto res_issue = [&](int i) {
+        int rm, rn;
+        tile_of(i, rm, rn);
         if (lane == 0) {
           mbar_expect_tx(rbar, 4096u);
-          tma_load_2d(slot, &tmR, (tile % tiles_n) * BN + part * 64, (tile / tiles_n) * TM + rank * BM + quarter * 32, rbar);
+          tma_load_2d(slot, &tmR, rn * BN + part * 64, rm * TM + rank * BM + quarter * 32, rbar);
         }
         res_pending = true;
       };
-      auto res_wanted = [&](int tile) { return tile < num_tiles && (tile % tiles_n) * BN + part * 64 < p.N; };
+      // the residual slab of this worker's i-th tile is wanted if that tile exists and this warp's columns lie in it
+      auto res_wanted = [&](int i) {
+        int rm, rn;
+        return tile_of(i, rm, rn) && rn * BN + part * 64 < p.N;
+      };
       const bool tma_res = RES != 0 && p.use_tma_res != 0 && p.residual != nullptr;
-      if (RES != 0 && tma_res && res_wanted(worker)) res_issue(worker);
-      const bool mish8 = O8 != 0 && p.act == kActMish && p.residual == nullptr;
+      if (RES != 0 && tma_res && res_wanted(0)) res_issue(0);
+      const bool mish8 = O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0;
+      // LNA: the epilogue warps are idle most of a tile, so they also normalise the rows of A. Warp ew owns rows ew,
+      // ew + 16, ... (8 of this CTA's 128) of every row block: all of the worker's first block up front, then a
+      // slice of the NEXT block after each tile's store, finished well before the producer needs that block.
+      constexpr int kRowsPerWarp = BM / kEpiWarps;
+      const int ln_per_tile = (kRowsPerWarp + tiles_n - 1) / tiles_n;
+      if constexpr (LNA) {
+        if (worker < tiles_m) {
+          ln_prefetch_rows(p, (long long)worker * TM + rank * BM, BM, ew, kEpiWarps, lane, 0, kRowsPerWarp);
+          if (worker + num_workers < tiles_m)     // the first slice of the second block, normalised after the first tile
+            ln_prefetch_rows(p, (long long)(worker + num_workers) * TM + rank * BM, BM, ew, kEpiWarps, lane, 0, ln_per_tile);
+          ln_rows_of_block(p, (long long)worker * TM + rank * BM, BM, ew, kEpiWarps, lane);
+        }
+        ln_signal_block_done(ln_counter, lane);
+      }
+      // at the start of a tile: prefetch the slice that will be normalised after the NEXT tile
+      auto ln_prefetch_ahead = [&](int cur_mi, int cur_ni) {
+        if constexpr (LNA) {
+          int nni = cur_ni + 1, nmi = cur_mi + num_workers;      // the slice after tile (cur_mi, cur_ni + 1) belongs to block nmi
+          if (nni >= tiles_n) { nni = 0; nmi += num_workers; }   // ... or, after this block's last tile, to the block after
+          const int j0 = nni * ln_per_tile;
+          if (j0 < kRowsPerWarp && nmi < tiles_m) {
+            const int cnt = (j0 + ln_per_tile <= kRowsPerWarp) ? ln_per_tile : kRowsPerWarp - j0;
+            ln_prefetch_rows(p, (long long)nmi * TM + rank * BM, BM, ew, kEpiWarps, lane, j0, cnt);
+          }
+        }
+      };
+      auto ln_step = [&](int cur_mi, int cur_ni) {
+        if constexpr (LNA) {
+          const int j0 = cur_ni * ln_per_tile;
+          const int nmi = cur_mi + num_workers;
+          if (j0 < kRowsPerWarp && nmi < tiles_m) {
+            const int cnt = (j0 + ln_per_tile <= kRowsPerWarp) ? ln_per_tile : kRowsPerWarp - j0;
+            ln_rows_of_block(p, (long long)nmi * TM + rank * BM, BM, ew, kEpiWarps, lane, j0, cnt);
+            if (j0 + cnt == kRowsPerWarp) ln_signal_block_done(ln_counter, lane);
+          }
+        }
+      };
       bool alive = true;
       int local = 0;
-      for (int t = worker; t < num_tiles; t += num_workers, ++local) {
+      int mi = 0, ni = 0;
+      for (; tile_of(local, mi, ni); ++local) {
         const int as = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
-        const int m0 = (t / tiles_n) * TM + rank * BM;   // first row of this CTA's accumulator half
-        const int n0 = (t % tiles_n) * BN;
+        const int m0 = mi * TM + rank * BM;   // first row of this CTA's accumulator half
+        const int n0 = ni * BN;
         // this tile's bias slice goes to shared memory while the MMAs are still running
         if (p.bias != nullptr) {
           for (int e = et; e < BN; e += kEpiWarps * 32) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
@@ -312,6 +532,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int e = et; e < BN; e += kEpiWarps * 32) cs_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.col_scale + n0 + e) : 0.0f;
         }
         asm volatile("bar.sync 1, 512;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
+        ln_prefetch_ahead(mi, ni);
         if (alive && !mbar_wait(tfull_bar(as), aph)) {
           if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
           alive = false;           // keep iterating so that the named barrier above stays balanced
@@ -328,15 +549,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
             else mbar_arrive(tempty_bar(as));
           }
-          if (RES != 0 && tma_res && res_wanted(t + num_workers)) {
+          if (RES != 0 && tma_res && res_wanted(local + 1)) {
             if (lane == 0) bulk_wait_read0();
-            res_issue(t + num_workers);
+            res_issue(local + 1);
           }
+          ln_step(mi, ni);
           continue;
         }
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(as * BN + part * 64);
-        uint32_t accA[16], accB[16];
-        tmem_ld_32x16(taddr, accA);
         const int row = m0 + quarter * 32 + lane;
         const bool row_ok = row < p.M;
         const int rrow = p.res_mod > 0 ? row % p.res_mod : row;
@@ -347,7 +567,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!mbar_wait(rbar, rph)) {
             if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
             alive = false;
-            tmem_ld_wait();
             continue;
           }
           rph ^= 1u;
@@ -358,18 +577,29 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         const bool direct_res = p.residual != nullptr && !(RES != 0 && tma_res) && row_ok;
         const bool res_vec = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
-        tmem_ld_wait_for(accA);
-        // four pieces of 16 columns; the TMEM load of piece i+1 is in flight while piece i is worked on
+        // two TMEM loads of 32 columns, each waited for before anything else touches its registers (a tcgen05.ld
+        // fills them asynchronously); each half is then worked on as two pieces of 16 columns
+        uint32_t acc[32];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          uint32_t (&cur)[16] = (i & 1) ? accB : accA;
-          uint32_t (&nxt)[16] = (i & 1) ? accA : accB;
-          if (i < 3) tmem_ld_32x16(taddr + 16u * (i + 1), nxt);
+          if ((i & 1) == 0) {
+            tmem_ld_32x32(taddr + 16u * i, acc);
+            tmem_ld_wait();
+            if (i == 2) {
+              // the last columns sit in registers: the accumulator buffer goes back to the MMA warp
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
+                else mbar_arrive(tempty_bar(as));
+              }
+            }
+          }
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            if constexpr (KIND == kKindI8) v[j] = static_cast<float>(static_cast<int>(cur[j])) * a_scale;
-            else v[j] = __uint_as_float(cur[j]) * a_scale;
+            if constexpr (KIND == kKindI8) v[j] = static_cast<float>(static_cast<int>(acc[(i & 1) * 16 + j])) * a_scale;
+            else v[j] = __uint_as_float(acc[(i & 1) * 16 + j]) * a_scale;
           }
           if constexpr (KIND == kKindI8) {
             if (p.col_scale != nullptr) {
@@ -466,16 +696,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
             }
           }
-          if (i < 3) tmem_ld_wait_for(nxt);
-          if (i == 2) {
-            // the last piece sits in registers: the accumulator buffer goes back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(as), 0));   // the leader's barrier
-              else mbar_arrive(tempty_bar(as));
-            }
-          }
         }
         fence_proxy_async_smem();   // every writing lane, before the barrier (the documented order)
         __syncwarp();
@@ -484,11 +704,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_store_2d(&tmC, slot, c0, m0 + quarter * 32);
           bulk_commit();
         }
+        ln_step(mi, ni);
         if (RES != 0 && tma_res) {
-          const int nt = t + num_workers;
-          if (res_wanted(nt)) {
+          if (res_wanted(local + 1)) {
             if (lane == 0) bulk_wait_read0();   // the store above has read the buffer: the next residual slab may land
-            res_issue(nt);
+            res_issue(local + 1);
           }
         }
       }
@@ -585,7 +805,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // activation: the switch sits outside the element loop so that the 32 independent
             // evaluations interleave
             // Mish into an e4m3 output runs on packed f16 pairs at the conversion below
-            const bool mish8 = p.act == kActMish && p.out_dtype == kOutE4M3 && p.residual == nullptr;
+            const bool mish8 = p.act == kActMish && p.out_dtype == kOutE4M3 && p.residual == nullptr && p.precise_act == 0;
             if (mish8) {
             } else if (p.act == kActMish) {
   #pragma unroll

@@ -75,14 +75,19 @@ inline bool out_map_ok(const GemmParams& p) {
          (static_cast<uint64_t>(p.N) * oesz) % 16 == 0;
 }
 
-template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0>
+// The fused-LayerNorm GEMM gives every CTA pair whole blocks of 256 rows; it pays when each pair has several.
+inline bool gemm_can_fuse_ln(long long M, int N, int K, int num_sms) {
+  return N >= 256 && K <= 1024 && K % 8 == 0 && (M + 255) / 256 >= 2ll * (num_sms / 2);
+}
+
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8>;
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -114,11 +119,12 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     prm.use_tma_res = 1;
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
   if constexpr (PAIR) {
-    // one 2-CTA cluster per pair of SMs
-    const int pairs = tiles < num_sms / 2 ? tiles : num_sms / 2;
+    // one 2-CTA cluster per pair of SMs (LNA: a pair owns whole row blocks, so no more pairs than row blocks)
+    const int units = LNA ? (a.p.M + Cfg::TM - 1) / Cfg::TM : tiles;
+    const int pairs = units < num_sms / 2 ? units : num_sms / 2;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -126,10 +132,10 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
   } else {
     const int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tn_kernel<BN, KIND, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
+    gemm_tn_kernel<BN, KIND, 0, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
     return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
   }
 }
@@ -141,6 +147,17 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   if (a.p.N <= 64) bn = 64;
   else if (a.p.N <= 128) bn = 128;
   else if (tiles_m * ((a.p.N + 255) / 256) < num_sms) bn = 128;  // small batch: more, smaller tiles
+  if (a.p.ln_y != nullptr) {
+    // A = LayerNorm(ln_y), normalised inside the kernel (f16 / e4m3 operands, no TMA-fetched residual)
+    if (KIND == kKindI8 || !gemm_can_fuse_ln(a.p.M, a.p.N, a.p.K, num_sms) || !out_map_ok(a.p) || a.p.col_scale != nullptr ||
+        a.p.ln_w16 == nullptr || a.p.ln_b16 == nullptr || (KIND == kKindF8 ? a.p.ln_x8 == nullptr : a.p.ln_x == nullptr) ||
+        a.p.ln_ldy % 8 != 0 || (reinterpret_cast<uintptr_t>(a.p.ln_y) & 15) != 0)
+      return kErrUnsupported;
+    if constexpr (KIND != kKindI8) {
+      return a.p.out_dtype == kOutE4M3 ? gemm_launch_t<256, KIND, 1, 0, 1, 1>(a, num_sms, stream)
+                                       : gemm_launch_t<256, KIND, 1, 0, 0, 1>(a, num_sms, stream);
+    }
+  }
   // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&
       (a.p.col_scale == nullptr || KIND == kKindI8)) {

@@ -30,6 +30,8 @@ class EngineConfig:
     chunk: int = 0
     pos_embed: int = 0
     lm_vocab: int = 0
+    fuse_layernorm: int = L.FUSE_LN_AUTO
+    precision: int = 0
 
     @staticmethod
     def reference_value_q(n_layers=10, d_model=512, d_ff=736, n_heads=8, **kw):

@@ -84,7 +84,26 @@ typedef struct crl_config {
   int32_t chunk;            /* positions processed per pass over the layers; 0 = library default */
   int32_t pos_embed;        /* 1: add the `pe` table [>=64, d] to the embedded tokens (model_bis.py:363-366) */
   int32_t lm_vocab;         /* CRL_POLICY_LM_HEAD: rows of lm_head.weight (1929 in the reference's scripts) */
+  int32_t fuse_layernorm;   /* CRL_FUSE_LN_AUTO (0): large passes of post-LN networks run the per-block LayerNorms inside
+                               the ff1 / QKV GEMM kernels; CRL_FUSE_LN_OFF: always as separate row passes */
+  int32_t precision;        /* bit mask of CRL_PREC_*; 0 = the fastest arithmetic of the chosen dtype */
 } crl_config;
+
+enum { CRL_FUSE_LN_AUTO = 0, CRL_FUSE_LN_OFF = 1 };
+/* Precision switches. The FP8 engine (model_fp8.py:43-140: per-tensor e4m3 linears, everything else in higher
+ * precision) takes several shortcuts around its e4m3 GEMMs by default; each bit takes one of them back, so that its
+ * cost in accuracy and speed can be measured on its own:
+ *   QKV_F16        Q, K, V and the smolgen bias tile cross HBM as f16 (default: e4m3 with one scale each)
+ *   LN_F32         LayerNorm with two-pass fp32 statistics and fp32 affine (default on large passes: one-pass
+ *                  statistics, f16 affine); also keeps the LayerNorms out of the GEMM kernels
+ *   MISH_F32       Mish of the ff1 epilogue in fp32 (default for e4m3 outputs: packed f16 pairs)
+ *   ATTN_F32       attention scores accumulated and soft-maxed in fp32 (default: f16 accumulate, packed-f16
+ *                  softmax); implies QKV_F16
+ *   FFN_F16        ff1 / ff2 on f16 operands (a mixed engine: only the attention GEMMs stay e4m3)
+ *   ATTN_GEMM_F16  QKV projection / out-projection on f16 operands (only the FFN GEMMs stay e4m3)
+ * LN_F32 and ATTN_F32 also apply to the FP16 and INT8 engines. */
+enum { CRL_PREC_QKV_F16 = 1, CRL_PREC_LN_F32 = 2, CRL_PREC_MISH_F32 = 4, CRL_PREC_ATTN_F32 = 8, CRL_PREC_FFN_F16 = 16,
+       CRL_PREC_ATTN_GEMM_F16 = 32 };
 
 /* One forward call. Stands for BT4.forward / get_batch_position_values (new_paradigm/value.py:155-212,
  * 275-317) and the server's bt4(X)['policy'] + mask + softmax (Leela/server.py:28-34,54-56).
@@ -220,6 +239,18 @@ typedef struct crl_linear_args {
   const float* col_scale;
   int* device_status;      /* >= 4 ints of device memory, zero before the call */
   void* stream;
+  /* Optional fused LayerNorm (all null / 0 = off): A is LayerNorm(ln_y) * ln_weight + ln_bias (eps 1e-5, the
+   * nn.LayerNorm in front of a Linear: new_paradigm/value.py:58-75), computed inside the GEMM kernel. ln_y is
+   * [m, k] f16 with row pitch k; ln_weight / ln_bias are [k] f16; the normalised rows are written to ln_x ([m, k]
+   * f16, required for f16 operands) and ln_x8 ([m, k] e4m3 of the rows times ln_out8_scale, required for e4m3
+   * operands), and `a` must point at the one the GEMM consumes. Needs m >= 256 x the SM count, k <= 1024,
+   * n >= 256 and a 16-bit or 8-bit output; CRL_ERR_UNSUPPORTED otherwise. */
+  const void* ln_y;
+  const void* ln_weight;
+  const void* ln_bias;
+  void* ln_x;
+  void* ln_x8;
+  float ln_out8_scale;
 } crl_linear_args;
 int crl_linear_ex(const crl_linear_args* args);
 

@@ -18,6 +18,7 @@ Tap points ("sites") that can be switched one by one, named after the GEMM whose
   ff1      FFN input and the ff1 weight
   ff2      FFN hidden activation (after the activation function) and the ff2 weight
   compress smolgen's per-token compression d -> 32 (shares the rounded layer input with qkv)
+  bias_gemm the last smolgen product [B*H, gen] x [4096, gen]^T: the normalised generator rows and the shared weight
 plus two storage roundings of the FP8 engine that are not GEMM operands:
   qkv_store  Q, K, V written as e4m3 with one scale and read back by attention
   bias_tile  the smolgen 64 x 64 bias written as e4m3 with one scale
@@ -36,7 +37,7 @@ import torch.nn.functional as F
 from . import bt4spec
 
 E4M3_MAX = 448.0
-ALL_GEMM_SITES = ("qkv", "out", "ff1", "ff2", "compress")
+ALL_GEMM_SITES = ("qkv", "out", "ff1", "ff2", "compress", "bias_gemm")
 ALL_FP8_SITES = ALL_GEMM_SITES + ("qkv_store", "bias_tile")
 
 
@@ -152,7 +153,16 @@ class QuantSpec:
         c = self._linear(l, "compress", x, "in").reshape(b, -1)
         h1 = sg.ln1(bt4spec.activation(sg.dense1(c), cfg.act))
         h2 = bt4spec.activation(sg.dense2(h1), cfg.act).view(b, cfg.n_heads, cfg.smolgen_gen)
-        bias = self.spec.smolgen_shared(sg.ln2(h2))
+        gen = sg.ln2(h2)
+        if record is not None:
+            record["gen"] = max(record.get("gen", 0.0), gen.abs().max().item())
+        if self._active(l, "bias_gemm") and self.fmt == "e4m3":
+            if "shared" not in self._wq:
+                w = self.spec.smolgen_shared.weight.detach()
+                self._wq["shared"] = round_e4m3(w, e4m3_mult(w.abs().amax()))
+            bias = F.linear(round_e4m3(gen, e4m3_mult(self.amax[l]["gen"])), self._wq["shared"])
+        else:
+            bias = self.spec.smolgen_shared(gen)
         if record is not None:
             record["bias"] = max(record.get("bias", 0.0), bias.abs().max().item())
         if self._active(l, "bias_tile") and self.fmt == "e4m3":

@@ -486,50 +486,171 @@ def test_value_driven_move_selection_matches_oracle():
         model.get_best_move_value("1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17")
 
 
-def test_benchmark_shape_accuracy_against_fp32_oracle():
-    """The network the throughput is quoted on (15 blocks, d 1024, 32 heads, smolgen) on 256 seeded playout
-    positions against the FP32 oracle. FP16 meets its bars (logits within 2e-2, WDL within 1e-2, top-1 >= 99 %).
-    FP8 and INT8 meet the WDL bar (3e-2) but NOT the 99 % top-1 bar on these random-init weights: the reference's
-    best and second-best legal logits are a median 0.04 apart (logit std 0.19) while fifteen layers of e4m3 / int8
-    GEMMs leave an rms logit error of ~0.02, so the arg-max flips on close calls (measured 0.91 / 0.97). The
-    floors below only guard against regressions; where the reference's margin exceeds 0.15 the agreement is
-    asserted at 99 %."""
+FENS = ["r3k2r/p1ppqpb1/bn2pnp1/3PN3/1p2P3/2N2Q1p/PPPBBPPP/R3K2R w KQkq - 0 1",
+        "rnbqkbnr/ppp1pppp/8/8/3pP3/8/PPPP1PPP/RNBQKBNR b KQkq e3 0 2",
+        "8/P7/8/8/8/8/k6p/4K3 w - - 0 1", "8/P7/8/8/8/8/k6p/4K3 b - - 0 1"]
+
+
+def _check_policy_move(model, logits_of, fen, planes, bits, mirrored):
+    """get_move_from_fen_no_thinking against the oracle's masked logits of the same input (model_bis.py:373-392)."""
+    from chessrl_b200 import positions
+    ref = logits_of(planes)                                                     # [1, 1929] fp32 oracle logits
+    legal = torch.from_numpy(np.unpackbits(bits.numpy(), axis=1, bitorder="little")[:, :1929].astype(bool))
+    masked = ref + (1 - legal.float()) * -999
+    unview = (lambda m: positions.mirror_uci(m)) if mirrored else (lambda m: m)
+    legal_moves = {unview(vocab.policy_index[i]) for i in torch.nonzero(legal[0]).flatten().tolist()}
+    # T = 0: the arg-max of the masked logits (a near-tie within the FP16 tolerance may resolve either way)
+    move = model.get_move_from_fen_no_thinking(fen, T=0)
+    best = masked[0].argmax().item()
+    if move != unview(vocab.policy_index[best]):
+        other = [i for i in range(1929) if unview(vocab.policy_index[i]) == move]
+        assert other and masked[0, best] - masked[0, other[0]] <= 2 * POLICY_TOL
+    assert move in legal_moves
+    # T > 0: distribution = softmax(masked / T), the draw lands on a legal move and is reproducible
+    for T in (0.5, 1.0):
+        g = torch.Generator().manual_seed(11)
+        m1, probs = model.get_move_from_fen_no_thinking(fen, T=T, return_probs=True, generator=g)
+        m2 = model.get_move_from_fen_no_thinking(fen, T=T, generator=torch.Generator().manual_seed(11))
+        assert m1 == m2 and m1 in legal_moves
+        want = torch.softmax(masked / T, -1)
+        assert probs.shape == (1, 1929) and (probs.cpu() - want).abs().max() <= 1e-2
+        assert float(probs.cpu()[~legal].sum()) <= 1e-6
+        u = torch.rand(1, generator=torch.Generator().manual_seed(11)).numpy()
+        idx, margin = vocab.choose_moves(probs.cpu().numpy(), True, 1.0, u)
+        assert m1 == unview(vocab.policy_index[int(idx[0])]) or margin[0] < 1e-3
+    move, onehot = model.get_move_from_fen_no_thinking(fen, T=0, return_probs=True)
+    assert float(onehot.sum()) == 1.0 and unview(vocab.policy_index[int(onehot.argmax())]) == move
+    # force_legal=False: the raw arg-max, legal or not
+    raw = model.get_move_from_fen_no_thinking(fen, T=0, force_legal=False)
+    raw_best = ref[0].argmax().item()
+    assert raw == unview(vocab.policy_index[raw_best]) or ref[0, raw_best] - ref[0].topk(2).values[1] <= 2 * POLICY_TOL
+
+
+def test_get_move_from_fen_no_thinking_on_the_three_modules():
+    """The board-only move choice every metrics script of the reference calls (model_bis.py:358-398,
+    new_paradigm/value.py:214-243), on the 19-plane BT4, the decoder GPT and the 112-plane BT4: legal mask with
+    knight promotions folded, -999 push-down, arg-max / temperature draw, UCI string out."""
+    from chessrl_b200 import BT4, BT4Planes19, GPT, GPTConfig, positions
+    from oracle import gptspec
+    # 19-plane BT4 (value.py)
+    c19 = bt4spec.SpecConfig.reference_value(2, 128, 192, 4)
+    s19 = bt4spec.BT4Spec(c19)
+    sd = bt4spec.seeded_state_dict(s19, seed=31)
+    s19.load_state_dict(sd)
+    s19.eval()
+    m19 = BT4Planes19(2, 128, 192, 4)
+    m19.load_state_dict(sd)
+    # decoder GPT (model_bis.py)
+    gcfg = gptspec.GPTConfig(256, 1929, 2, 2, 128)
+    gs = gptspec.GPTSpec(gcfg)
+    from test_oracle_golden import gpt_golden_state_dict
+    gsd = gpt_golden_state_dict(gs, 32)
+    gs.load_state_dict(gsd)
+    gs.eval()
+    gpt = GPT(GPTConfig(256, 1929, 2, 2, 128))
+    gpt.load_state_dict(gsd)
+    # 112-plane BT4 (value_q.py)
+    c112 = bt4spec.SpecConfig.reference_value_q(2, 128, 192, 4)
+    s112 = bt4spec.BT4Spec(c112)
+    sd112 = bt4spec.seeded_state_dict(s112, seed=33)
+    s112.load_state_dict(sd112)
+    s112.eval()
+    m112 = BT4(2, 128, 192, 4)
+    m112.load_state_dict(sd112)
+    for fen in FENS:
+        p19 = torch.from_numpy(positions.fen_to_tensor(fen))[None]
+        bits = torch.from_numpy(positions.legal_mask_1929(fen))[None]
+        with torch.no_grad():
+            _check_policy_move(m19, lambda x: s19.forward_all(x.view(1, 64, 19))["policy"], fen, p19, bits, False)
+            _check_policy_move(gpt, lambda x: gs.board_logits(x), fen, p19, bits, False)
+            black = fen.split()[1] == "b"
+            view_bits = torch.from_numpy(positions.legal_mask_1929(positions.mirror_fen(fen) if black else fen))[None]
+            p112 = torch.from_numpy(positions.fen_to_planes112(fen)).float()[None]
+            _check_policy_move(m112, lambda x: s112.forward_all(x.view(1, 64, 112))["policy"], fen, p112, view_bits, black)
+    with pytest.raises(ValueError):
+        m19.get_move_from_fen_no_thinking("1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17")   # checkmate
+
+
+def test_q_value_entry_points_and_many_position_scoring():
+    """value_q.py:244-347 on the 112-plane module: tanh Q per FEN (shape [B, 1], scalar for one), successors scored
+    as -Q for White to move / +Q for Black, and the many-position entry = the per-position calls, one engine call."""
+    from chessrl_b200 import BT4, BT4Planes19, positions
+    c112 = bt4spec.SpecConfig.reference_value_q(2, 128, 192, 4)
+    s112 = bt4spec.BT4Spec(c112)
+    sd = bt4spec.seeded_state_dict(s112, seed=41)
+    s112.load_state_dict(sd)
+    s112.eval()
+    m = BT4(2, 128, 192, 4)
+    m.load_state_dict(sd)
+    x = torch.from_numpy(np.stack([positions.fen_to_planes112(f) for f in FENS])).float()
+    with torch.no_grad():
+        want = s112.forward_all(x.view(len(FENS), 64, 112))["q"]
+    got = m.get_batch_position_values(FENS)
+    assert got.shape == (len(FENS), 1) and (got.cpu() - want).abs().max() <= WDL_TOL
+    one = m.get_position_value(FENS[1])
+    assert one.dim() == 0 and abs(float(one) - float(want[1])) <= WDL_TOL
+    assert m.get_batch_position_values([]).shape == (0, 1)
+    for fen in FENS[:2]:
+        ucis, values = m.calculate_move_values(fen)
+        _, succ, _ = positions.successors(fen, planes19=False)
+        sx = torch.from_numpy(np.stack([positions.fen_to_planes112(f) for f in succ])).float()
+        with torch.no_grad():
+            q = s112.forward_all(sx.view(len(succ), 64, 112))["q"].view(-1)
+        sign = -1.0 if fen.split()[1] == "w" else 1.0
+        assert (values.cpu() - sign * q).abs().max() <= WDL_TOL
+        assert m.get_best_move_value(fen, T=0) == ucis[int(values.argmax())]
+    many = m.calculate_move_values_many(FENS)
+    assert len(many) == len(FENS)
+    for fen, (ucis, values) in zip(FENS, many):
+        u1, v1 = m.calculate_move_values(fen)
+        assert ucis == u1 and (values - v1).abs().max() <= 1e-3
+    eng = m.engine()
+    before = eng.last_launch_count()
+    m.calculate_move_values_many(FENS)
+    assert eng.last_launch_count() == before                 # one engine call, whatever the number of positions
+    # the 19-plane module shares the machinery (value.py:319-354)
+    c19 = bt4spec.SpecConfig.reference_value(2, 128, 192, 4)
+    s19 = bt4spec.BT4Spec(c19)
+    sd19 = bt4spec.seeded_state_dict(s19, seed=42)
+    m19 = BT4Planes19(2, 128, 192, 4)
+    m19.load_state_dict(sd19)
+    many19 = m19.calculate_move_values_many(FENS[:3])
+    for fen, (ucis, values) in zip(FENS[:3], many19):
+        u1, v1 = m19.calculate_move_values(fen)
+        assert ucis == u1 and (values - v1).abs().max() <= 1e-3
+    assert m19.calculate_move_values_many(["1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17"])[0][0] == []
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_gemm_fused_layernorm_equals_separate_passes(dtype):
+    """Large passes of post-LN networks normalise inside the ff1 / QKV GEMM kernels. The fused warps use the
+    arithmetic of the stand-alone LayerNorm kernel, so switching the fusion off must not change a single bit."""
     from chessrl_b200 import Engine, EngineConfig, positions
     import chessrl_b200 as crl
-    torch.set_num_threads(max(torch.get_num_threads(), 8))
-    cfg = bt4spec.SpecConfig.baseline(15, 1024, 1536, 32, smolgen=True)
-    spec = bt4spec.BT4Spec(cfg)
-    sd = bt4spec.seeded_state_dict(spec, seed=5)
-    spec.load_state_dict(sd)
-    spec.eval()
-    n = 256
-    pos = positions.playout_positions(n, seed=77, max_plies=80)
-    with torch.no_grad():
-        ref = spec.forward_all(pos["planes112"].float().view(n, 64, 112))
-    legal = torch.from_numpy(np.unpackbits(pos["legal1858"].numpy(), axis=1, bitorder="little")[:, :1858].astype(bool))
-    ref_masked = bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal)
-    top2 = ref_masked.sort(-1, descending=True).values[:, :2]
-    clear = (top2[:, 0] - top2[:, 1]) > 0.15
-    assert int(clear.sum()) >= 10
-    floors = {crl.DTYPE_F16: (0.99, 1e-2), crl.DTYPE_F8E4M3: (0.85, 3e-2), crl.DTYPE_I8: (0.92, 3e-2)}
-    for dt, (floor, wtol) in floors.items():
-        eng = Engine(EngineConfig(dtype=dt, **cfg.to_dict()))
+    cfg = bt4spec.SpecConfig.baseline(3, 256, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=13)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    b = 4 * sms + 37                                        # 64 b rows: more than two 256-row blocks per CTA pair, ragged
+    pos = positions.playout_positions(b, seed=21)
+    planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
+    outs = []
+    for fuse in (crl.FUSE_LN_AUTO, crl.FUSE_LN_OFF):
+        eng = Engine(EngineConfig(dtype=dtype, fuse_layernorm=fuse, **cfg.to_dict()))
         eng.load_state_dict(sd)
-        x = pos["planes112"].cuda()
-        if dt == crl.DTYPE_F8E4M3:
-            eng.calibrate(x)
-        out = eng.forward(x, legal_mask=pos["legal1858"].cuda())
-        pol, wdl = out["policy"].float().cpu(), out["wdl"].cpu()
-        same = pol.argmax(-1) == ref_masked.argmax(-1)
-        agree, agree_clear = same.float().mean().item(), same[clear].float().mean().item()
-        werr = (wdl - torch.softmax(ref["wdl"], -1)).abs().max().item()
-        perr = (pol - ref_masked)[legal].abs().max().item()
-        print(f"benchmark shape, dtype {dt}: top-1 {agree:.4f} (clear margins {agree_clear:.4f}, {int(clear.sum())} positions), "
-              f"wdl err {werr:.3e}, policy max-abs err {perr:.3e}")
-        assert werr <= wtol and agree >= floor and agree_clear >= 0.99
-        if dt == crl.DTYPE_F16:
-            assert perr <= POLICY_TOL
+        if dtype == crl.DTYPE_F8E4M3:
+            eng.calibrate(planes[:256])
+        out = eng.forward(planes, legal_mask=bits)
+        torch.cuda.synchronize()
+        rc, st = eng.last_status()
+        assert rc == 0 and st == 0
+        outs.append((out["policy"].cpu(), out["wdl"].cpu(), eng.last_launch_count()))
         eng.close()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][2] == outs[1][2] - 2 * 3 + 1             # two LayerNorm launches fewer per block, the last block keeps its second
+    if dtype == 0:
+        ref = oracle_out(cfg, sd, pos["planes112"].float().view(b, 64, 112)[:64])
+        legal = torch.from_numpy(np.unpackbits(pos["legal1858"].numpy()[:64], axis=1, bitorder="little")[:, :1858].astype(bool))
+        assert (outs[0][0][:64] - bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal))[legal].abs().max() <= POLICY_TOL
 
 
 def test_determinism_and_output_guards():

@@ -110,6 +110,17 @@ def e4m3_step(x):
     return torch.exp2(e - 3)
 
 
+def assert_close_elementwise(got, want, tol):
+    """Every element within its own tolerance; on failure name the worst offenders (row, column, got, want)."""
+    bad = ~((got - want).abs() <= tol)
+    if bool(bad.any()):
+        idx = torch.nonzero(bad)[:6].tolist()
+        rows = sorted({i for i, _ in torch.nonzero(bad)[:20000].tolist()})
+        raise AssertionError(f"{int(bad.sum())} of {bad.numel()} elements off; first: "
+                             + ", ".join(f"[{i},{j}] got {float(got[i, j]):.5g} want {float(want[i, j]):.5g}" for i, j in idx)
+                             + f"; rows touched (first 12): {rows[:12]} ... {len(rows)} rows")
+
+
 FP8_SHAPES = [(4096, 3072, 1024), (16384, 1024, 1536), (19001, 520, 1024), (130 * 64, 8200, 256)]
 
 
@@ -138,7 +149,8 @@ def test_e4m3_pair_kernel_e4m3_out_with_out_scale(lib, m, n, k):
     ref = (alpha * (a.float() @ w.float().t()) + bias) * out_scale
     c = e4m3_decode(call_ex(lib, 1, a, w, 2, bias=bias, alpha=alpha, out_scale=out_scale, ldc=n + (16 - n % 16) % 16 + 16))
     ref = ref.clamp(-448, 448)
-    assert bool(((c - ref).abs() <= 0.5 * e4m3_step(ref) + 1e-3 * ref.abs() + 1e-6).all())
+    order = 1e-6 * alpha * out_scale * (a.float().abs() @ w.float().abs().t())
+    assert_close_elementwise(c, ref, 0.5 * e4m3_step(ref) + 1e-3 * ref.abs() + order)
 
 
 def test_e4m3_pair_kernel_mish_packed_epilogue(lib):
@@ -154,7 +166,7 @@ def test_e4m3_pair_kernel_mish_packed_epilogue(lib):
     c = e4m3_decode(call_ex(lib, 1, a, w, 2, bias=bias, alpha=alpha, act=2, out_scale=out_scale))
     ref = ref.clamp(-448, 448)
     tol = 0.5 * e4m3_step(ref) + 6e-3 * ref.abs() + 2e-3     # f16 arithmetic around zero: 2e-3 absolute after scaling
-    assert bool(((c - ref).abs() <= tol).all())
+    assert_close_elementwise(c, ref, tol)
 
 
 @pytest.mark.parametrize("m,n,k,kind", [(16384, 1024, 1024, 1), (16384 + 77, 1024, 1536, 1), (16384, 1024, 1024, 0),
@@ -215,4 +227,79 @@ def test_f16_pair_kernel_to_e4m3(lib):
     out_scale = 100.0
     ref = ((a.float() @ w.float().t()) * out_scale).clamp(-448, 448)
     c = e4m3_decode(call_ex(lib, 0, a, w, 2, out_scale=out_scale))
-    assert bool(((c - ref).abs() <= 0.5 * e4m3_step(ref) + 1e-3 * ref.abs() + 1e-6).all())
+    # fp32 sums of 256 products of either sign: two summation orders differ by ~1e-6 of the sum of magnitudes, which
+    # decides the rounding of results next to zero
+    order = 1e-6 * (a.float().abs() @ w.float().abs().t()) * out_scale
+    assert_close_elementwise(c, ref, 0.5 * e4m3_step(ref) + 1e-3 * ref.abs() + order)
+
+
+@pytest.mark.parametrize("kind,out,n", [(1, 2, 1536), (1, 2, 3072), (0, 0, 1536), (1, 0, 512)])
+def test_layernorm_fused_into_the_gemm(lib, kind, out, n):
+    """LNA kernels: the rows of A are LayerNorm(y) computed by the GEMM kernel's own warps a row block ahead of the
+    MMAs. Checked in two steps: the normalised rows it writes (f16, and e4m3 with a scale) against torch's
+    layer_norm, then the product against an fp32 matmul of exactly those written rows (so the second check is as
+    tight as for a plain GEMM). M is ragged and large enough for every CTA pair to own several row blocks."""
+    import ctypes
+    from chessrl_b200 import _lib as L
+    torch.manual_seed(n + kind)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    m, k = 256 * sms + 256 * 40 + 77, 1024
+    y = (torch.randn(m, k, device="cuda") * 1.3 + 0.2).half()
+    gamma = (1.0 + 0.1 * torch.randn(k, device="cuda")).half()
+    beta = (0.1 * torch.randn(k, device="cuda")).half()
+    w = torch.randn(n, k, device="cuda")
+    w = w.to(torch.float8_e4m3fn) if kind == 1 else (w * 0.05).half()
+    bias = torch.randn(n, device="cuda")
+    x16 = torch.zeros(m, k, device="cuda", dtype=torch.float16)
+    x8 = torch.zeros(m, k, device="cuda", dtype=torch.uint8)
+    s8 = 448.0 / 6.0
+    c = torch.zeros(m + 2, n, device="cuda", dtype=torch.uint8 if out == 2 else torch.float16)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a = L.LinearArgs()
+    a.kind, a.out_dtype = kind, out
+    a.a, a.lda = (x8 if kind == 1 else x16).data_ptr(), k
+    a.w, a.ldw, a.c, a.ldc = w.data_ptr(), k, c.data_ptr(), n
+    a.m, a.n, a.k = m, n, k
+    a.bias = bias.data_ptr()
+    a.alpha = 1.0 / (s8 * 8.0) if kind == 1 else 1.0
+    a.out_scale = 20.0
+    a.device_status = status.data_ptr()
+    a.ln_y, a.ln_weight, a.ln_bias = y.data_ptr(), gamma.data_ptr(), beta.data_ptr()
+    a.ln_x, a.ln_x8, a.ln_out8_scale = x16.data_ptr(), x8.data_ptr(), s8
+    rc = lib.crl_linear_ex(ctypes.byref(a))
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status[0]) == 0, (rc, int(status[0]))
+    want_x = torch.nn.functional.layer_norm(y.float(), (k,), gamma.float(), beta.float(), 1e-5)
+    assert (x16.float() - want_x).abs().max() <= 6e-3                       # f16 affine: a few f16 steps at |x| ~ 4
+    got8 = e4m3_decode(x8)
+    ref8 = (x16.float() * s8).clamp(-448, 448)
+    assert_close_elementwise(got8, ref8, 0.5 * e4m3_step(ref8) + 2e-3 * ref8.abs() + 1e-6)
+    a_used = got8 if kind == 1 else x16.float()
+    ref = a.alpha * (a_used @ w.float().t()) + bias
+    assert bool((c[m:] == 0).all()), "rows beyond M were written"
+    if out == 2:
+        ref = (ref * 20.0).clamp(-448, 448)
+        order = 1e-6 * a.alpha * 20.0 * (a_used.abs() @ w.float().abs().t())          # summation-order slack, see above
+        assert_close_elementwise(e4m3_decode(c[:m]), ref, 0.5 * e4m3_step(ref) + 1e-3 * ref.abs() + order)
+    else:
+        assert_close_elementwise(c[:m].float(), ref, torch.full_like(ref, 2e-3 * ref.abs().max().item()))
+
+
+def test_layernorm_fusion_is_refused_where_it_cannot_run(lib):
+    """Too few row blocks for the CTA pairs, or int8 operands: CRL_ERR_UNSUPPORTED, nothing launched."""
+    import ctypes
+    from chessrl_b200 import _lib as L
+    m, n, k = 4096, 1024, 1024
+    y = torch.zeros(m, k, device="cuda", dtype=torch.float16)
+    g = torch.ones(k, device="cuda", dtype=torch.float16)
+    x16 = torch.zeros_like(y)
+    w = torch.zeros(n, k, device="cuda", dtype=torch.float16)
+    c = torch.full((m, n), 3.0, device="cuda", dtype=torch.float16)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a = L.LinearArgs()
+    a.kind, a.out_dtype, a.a, a.lda, a.w, a.ldw, a.c, a.ldc = 0, 0, x16.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
+    a.m, a.n, a.k, a.alpha, a.device_status = m, n, k, 1.0, status.data_ptr()
+    a.ln_y, a.ln_weight, a.ln_bias, a.ln_x = y.data_ptr(), g.data_ptr(), g.data_ptr(), x16.data_ptr()
+    assert lib.crl_linear_ex(ctypes.byref(a)) == -8
+    torch.cuda.synchronize()
+    assert bool((c == 3.0).all())
