@@ -17,8 +17,8 @@ Small repeatable programs for a profiler capture (`-k regex:<kernel>`); they pri
         three launches, then 20 more timed with CUDA events
     python bench.py --case forward <f16|f8|i8> <positions> [chunk [fuse_layernorm [precision]]]
         the BT4-shaped forward pass: plain timing of three passes, then one pass with the library's per-launch
-        CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm 1 = LayerNorms as separate
-        passes; precision = CRL_PREC_* bit mask)
+        CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm 1 = LayerNorms inside the
+        ff1 / QKV GEMM kernels; precision = CRL_PREC_* bit mask)
 """
 import argparse
 import json

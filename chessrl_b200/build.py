@@ -15,7 +15,7 @@ LIB = os.path.join(HERE, "libchessrl_b200.so")
 SOURCES = ["engine.cu", "chess.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false",
+    "-shared", "-Xcompiler", "-fPIC",
 ]
 
 
@@ -32,7 +32,7 @@ def build(force=False, verbose=False):
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source_mtime():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    cmd = [nvcc] + list(NVCC_FLAGS)
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]

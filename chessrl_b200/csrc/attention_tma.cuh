@@ -1,9 +1,11 @@
-// Pipelined per-board attention for head_dim 32 (the widths the engine is benchmarked at): the same
-// math as attention.cuh, restructured so that HBM latency is hidden. Persistent CTAs, one per SM; every
-// warp runs its own two-stage pipeline over (board, head) items: one lane issues TMA box loads of the
-// Q, K, V tiles (64 x 64 bytes each, 64-byte swizzle) and of the 64 x 64 smolgen bias tile (f16 or
-// e4m3) for item i+1 while the warp computes item i; the context tile goes back through a swizzled
-// staging tile and a TMA store. Completion is tracked by per-warp mbarriers; waits are bounded.
+// Per-board attention for head_dim 32 (the widths the engine is benchmarked at): the same math as
+// attention.cuh with the loads and stores on the TMA unit. Persistent CTAs, one per SM; every warp walks its own
+// (board, head) items: one lane issues TMA box loads of the item's Q, K, V tiles (64 x 64 bytes each, 64-byte
+// swizzle) and of its 64 x 64 smolgen bias tile (f16 or e4m3) into the warp's own buffers, the warp waits for
+// them, computes, and sends the context tile back through the Q buffer and a TMA store. A warp's buffers are
+// single-stage: its load latency is covered by the other warps of the CTA, not by prefetching its next item
+// (the kernel is bound by its dependent ldmatrix / mma / exp chains, so more resident warps beat deeper buffers).
+// Completion is tracked by per-warp mbarriers; waits are bounded.
 #pragma once
 #include <cuda.h>
 #include "attention.cuh"

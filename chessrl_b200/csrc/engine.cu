@@ -373,10 +373,11 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
   p.yq = yq; p.yq_scale = yq_scale;
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
   ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * d * (2 + (y != nullptr ? 2 : 0) + (y8 != nullptr ? 1 : 0)));
-  if (yq == nullptr && gate_ea == nullptr && rows >= 8192 && (h->cfg.precision & CRL_PREC_LN_F32) == 0) {
+  if (gate_ea == nullptr && rows >= 8192 && (h->cfg.precision & CRL_PREC_LN_F32) == 0) {
     const long long want = (rows + 7) / 8;
     const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 2));
-    ln_rows_persistent_kernel<<<grid, 256, 0, s>>>(p);
+    if (yq != nullptr) ln_rows_persistent_kernel<true><<<grid, 256, 0, s>>>(p);
+    else ln_rows_persistent_kernel<false><<<grid, 256, 0, s>>>(p);
   } else {
     ln_rows_kernel<<<blocks, 256, 0, s>>>(p);
   }
@@ -387,7 +388,10 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
 
 int quant_rows_i8(crl_handle* h, const __half* x, long long rows, int cols, uint8_t* q, float* scale, cudaStream_t s) {
   ProfScope ps(h, s, kCatLayerNorm, 0.0, static_cast<double>(rows) * cols * 3);
-  quant_rows_i8_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(x, rows, cols, reinterpret_cast<int8_t*>(q), scale);
+  if (cols > 4096 || cols % 8 != 0) return fail(h, CRL_ERR_SHAPE, "per-token int8 rows are at most 4096 wide");
+  const long long want = (rows + 7) / 8;
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 8));
+  quant_rows_i8_kernel<<<grid, 256, 0, s>>>(x, rows, cols, reinterpret_cast<int8_t*>(q), scale);
   CRL_CUDA(h, cudaGetLastError());
   ++h->launches;
   return CRL_OK;
@@ -505,10 +509,10 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   const bool ctx8 = f8_attn;      // attention writes its context as e4m3 for an e4m3 out-projection
   int8_t* const xq = reinterpret_cast<int8_t*>(w.x8);
   const int act = act_of(c);
-  // Post-LN blocks on large passes: the LayerNorm in front of ff1 and the one in front of the next block's QKV
-  // projection run inside those GEMM kernels (their own warps normalise a row block ahead of the MMAs) instead of
-  // as separate passes over the rows.
-  const bool fuse_ln = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm != CRL_FUSE_LN_OFF &&
+  // Optional (crl_config.fuse_layernorm): post-LN blocks on large passes run the LayerNorm in front of ff1 and the one
+  // in front of the next block's QKV projection inside those GEMM kernels (their own warps normalise a row block
+  // ahead of the MMAs) instead of as separate passes over the rows.
+  const bool fuse_ln = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm == CRL_FUSE_LN_ON &&
                        (prec & CRL_PREC_LN_F32) == 0 && gemm_can_fuse_ln(M, std::min(3 * d, ff), d, h->num_sms);
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
@@ -934,7 +938,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
       c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
   if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3 && c.dtype != CRL_DTYPE_I8) return CRL_ERR_UNSUPPORTED;
-  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_OFF || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
+  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_ON || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
   if (c.dtype == CRL_DTYPE_I8 && (c.d_model % 16 != 0 || c.d_ff % 16 != 0)) return CRL_ERR_SHAPE;
   if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&

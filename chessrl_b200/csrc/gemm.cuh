@@ -59,6 +59,7 @@ struct GemmParams {
 constexpr int kGemmThreads = 576;   // TMA warp + MMA warp + 16 epilogue warps
 
 constexpr int kEpiWarps = 16;
+constexpr int kLnWarps = 6;          // LNA kernels: LayerNorm warps after the epilogue warps
 
 // PAIR = 1: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs. Each CTA stages
 // its own 128 rows of A and its own BN/2 rows of W, so a pair moves a third less data from L2 into
@@ -71,7 +72,7 @@ constexpr int kEpiWarps = 16;
 template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0>
 struct GemmCfg {
   static_assert(!LNA || PAIR, "the fused LayerNorm exists for CTA pairs only");
-  static constexpr int THREADS = kGemmThreads;
+  static constexpr int THREADS = kGemmThreads + (LNA ? 32 * kLnWarps : 0);
   static_assert(!(RES && O8), "the residual variant writes f16");
   static_assert(!PAIR || BN == 256, "pairs work on 256 x 256 tiles");
   static constexpr int BM = 128;           // rows per CTA
@@ -82,25 +83,29 @@ struct GemmCfg {
   static constexpr uint32_t A_BYTES = BM * 128;
   static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * 128;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  // bias [2][BN] f32; int8 adds the per-column scales [2][BN]
-  static constexpr uint32_t TAB_BYTES = ((PAIR && KIND != kKindI8) ? 2 : 4) * BN * 4;
+  // single CTAs stage the tile's bias [2][BN] and per-column scales [2][BN] in shared memory; pairs read them
+  // straight from global memory (L1-resident), which needs no barrier among the epilogue warps
+  static constexpr uint32_t TAB_BYTES = PAIR ? 0 : 4 * BN * 4;
   // per epilogue warp: pairs one slab (32 rows x 64 columns of the output type), single CTAs one 32 x 32 chunk
   static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : 4096) : 2048;
   // pairs: f16 slabs leave room for five 32 KB stages (four with the int8 scale table)
-  static constexpr int STAGES = PAIR ? ((!O8 && KIND == kKindI8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
+  // pairs: five 32 KB stages; the f16-output kernels with a fused LayerNorm give one up for its parameter table
+  static constexpr int STAGES = PAIR ? ((LNA && !O8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
                                      : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
+  static constexpr uint32_t LN_PRM_BYTES = LNA ? 4096 : 0;    // LayerNorm weight [1024] and bias [1024] as f16
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
   // after the stages: the tables, the per-warp slabs (1024-byte aligned: TMA swizzles by absolute address
   // bits), then the mbarriers (ring, accumulators, one per epilogue warp for its residual slab) + TMEM slot
   static constexpr uint32_t EPI_OFF = STAGES * STAGE_BYTES;
-  static constexpr uint32_t BAR_OFF = EPI_OFF + TAB_BYTES + kEpiWarps * SLOT_BYTES;
+  static constexpr uint32_t LN_PRM_OFF = EPI_OFF + TAB_BYTES + kEpiWarps * SLOT_BYTES;
+  static constexpr uint32_t BAR_OFF = LN_PRM_OFF + LN_PRM_BYTES;
   // barrier region: [0,128) ring (2 x STAGES <= 12) and accumulator (4) mbarriers, [128,144) the TMEM address slot,
-  // [144, 144 + 8 x 16) one mbarrier per epilogue warp (residual slab), then the LayerNorm progress counter
+  // [144, 144 + 8 x 16) one mbarrier per epilogue warp (residual slab), then the LayerNorm progress words
   static_assert(2 * STAGES + 4 <= 16, "the ring and accumulator barriers share 128 bytes");
   static constexpr uint32_t TMEM_SLOT_OFF = BAR_OFF + 128;
   static constexpr uint32_t RBAR_OFF = BAR_OFF + 144;
   static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 8;
-  static constexpr uint32_t USED_BYTES = LN_COUNTER_OFF + 16;
+  static constexpr uint32_t USED_BYTES = LN_COUNTER_OFF + 48;   // [0] epilogue warps' arrivals, [4 + w] blocks done by LayerNorm warp w
   static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + ((PAIR && (!O8 || STAGES > 5)) ? 496 : 896) /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
 };
@@ -156,35 +161,57 @@ __device__ __forceinline__ void store_one(void* C, int out_dtype, long long off,
       static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
 }
 
-// LayerNorm (eps 1e-5, affine) of rows [row0, row0 + nrows) of p.ln_y, shared among `nw` warps: warp `wi` owns rows
-// wi, wi + nw, ... and this call does its rows number j0 .. j0 + cnt - 1, with the next row's loads in flight while
-// one is normalised. Same arithmetic as
-// ln_rows_persistent_kernel (fp32 statistics, f16 affine), so a network gives the same bits whichever kernel
-// normalises a row. K <= 1024, K % 8 == 0.
-__device__ __forceinline__ void ln_rows_of_block(const GemmParams& p, long long row0, int nrows, int wi, int nw, int lane,
-                                                 int j0 = 0, int cnt = 1 << 20) {
+__device__ __forceinline__ uint4 ln_load_row_piece(const __half* src) {
+  uint4 u;      // streamed once: no L1 allocation
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(src));
+  return u;
+}
+
+// LayerNorm (eps 1e-5, affine) of rows [row0, row0 + nrows) of p.ln_y, shared among `nw` warps: warp `wi` takes rows
+// wi, wi + nw, ... with the next row's loads in flight while one is normalised. Same arithmetic as ln_rows_persistent_kernel (fp32 statistics, f16 affine), so a network gives
+// the same bits whichever kernel normalises a row. K <= 1024, K % 8 == 0.
+// One bulk L2 prefetch of a whole row of ln_y (a hint; issued by one lane).
+__device__ __forceinline__ void ln_prefetch_row(const GemmParams& p, long long row) {
+  if (row < p.M)
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ln_y + row * p.ln_ldy), "r"(uint32_t(p.K) * 2u) : "memory");
+}
+
+// `next_first` / `next_nw`: the warp's first row and row stride in the block it will normalise after this one (-1:
+// none). While row k is normalised, row k + 1 is on its way into registers and row k + 3 - of this block or the next -
+// is requested into L2: close enough ahead to still be there, far enough to hide the HBM round trip.
+__device__ __forceinline__ void ln_rows_of_block(const GemmParams& p, uint32_t prm_smem, long long row0, int nrows, int wi,
+                                                 int nw, int lane, long long next_first = -1, int next_nw = 1) {
   constexpr int NV = 4;
+  constexpr int kAhead = 3;
   const int d = p.K;
-  long long row = row0 + wi + (long long)j0 * nw;       // the warp's rows j0, j0 + 1, ... (of wi, wi + nw, ...)
-  long long end = (row0 + nrows < p.M) ? row0 + nrows : p.M;
-  if (cnt < (1 << 20)) {                                // at most cnt rows: the last one is row + (cnt - 1) * nw
-    const long long lim = row + (long long)(cnt - 1) * nw + 1;
-    if (lim < end) end = lim;
+  long long row = row0 + wi;                            // the warp's rows wi, wi + nw, ...
+  const long long end = (row0 + nrows < p.M) ? row0 + nrows : p.M;
+  // first value of the sequence wi, wi + nw, ... beyond the block: rows past it continue in the next block
+  const long long seq_end = row + ((end - row + nw - 1) / nw) * nw;
+  auto prefetch_ahead = [&](long long r) {
+    if (lane == 0) {
+      if (r < end) ln_prefetch_row(p, r);
+      else if (next_first >= 0) ln_prefetch_row(p, next_first + ((r - seq_end) / nw) * next_nw);
+    }
+  };
+  if (row >= end) {
+    if (next_first >= 0 && lane < kAhead) ln_prefetch_row(p, next_first + (long long)lane * next_nw);
+    return;
   }
-  if (row >= end) return;
   uint4 raw[NV], nxt[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int c = (i * 32 + lane) * 8;
-    raw[i] = c < d ? *reinterpret_cast<const uint4*>(p.ln_y + row * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
+    raw[i] = c < d ? ln_load_row_piece(p.ln_y + row * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
   }
   const __half2 s8 = __floats2half2_rn(p.ln_out8_scale, p.ln_out8_scale);
   for (; row < end; row += nw) {
     const long long nrow = row + nw;
+    prefetch_ahead(row + (long long)kAhead * nw);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = (i * 32 + lane) * 8;
-      nxt[i] = (nrow < end && c < d) ? *reinterpret_cast<const uint4*>(p.ln_y + nrow * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
+      nxt[i] = (nrow < end && c < d) ? ln_load_row_piece(p.ln_y + nrow * p.ln_ldy + c) : make_uint4(0u, 0u, 0u, 0u);
     }
     float sum = 0.0f, sq = 0.0f;
 #pragma unroll
@@ -209,11 +236,12 @@ __device__ __forceinline__ void ln_rows_of_block(const GemmParams& p, long long 
     for (int i = 0; i < NV; ++i) {
       const int c = (i * 32 + lane) * 8;
       if (c < d) {
-        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.ln_w16 + c));
-        const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.ln_b16 + c));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+        uint4 w4, b4;      // this lane's 8 weight and 8 bias columns from the table in shared memory
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w4.x), "=r"(w4.y), "=r"(w4.z), "=r"(w4.w) : "r"(prm_smem + 2u * c));
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(b4.x), "=r"(b4.y), "=r"(b4.z), "=r"(b4.w) : "r"(prm_smem + 2048u + 2u * c));
         const __half2* wh = reinterpret_cast<const __half2*>(&w4);
         const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
         uint32_t o16[4];
         __half2 y2[4];
 #pragma unroll
@@ -241,42 +269,47 @@ __device__ __forceinline__ void ln_rows_of_block(const GemmParams& p, long long 
   }
 }
 
-// Hint: bring the warp's rows number j0 .. j0 + cnt - 1 of a row block into L2 (one bulk prefetch per row, issued
-// by lane j - j0), so that the loads of ln_rows_of_block find them there instead of paying an HBM round trip while
-// the accumulator of the next tile is waiting to be drained.
-__device__ __forceinline__ void ln_prefetch_rows(const GemmParams& p, long long row0, int nrows, int wi, int nw, int lane, int j0, int cnt) {
-  if (lane < cnt) {
-    const long long row = row0 + wi + (long long)(j0 + lane) * nw;
-    const long long end = (row0 + nrows < p.M) ? row0 + nrows : p.M;
-    if (row < end)
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.ln_y + row * p.ln_ldy), "r"(uint32_t(p.K) * 2u) : "memory");
-  }
-}
-
-// A warp's rows of a row block are written: order them before the TMA loads that will read them (generic-proxy
-// stores, async-proxy loads of the same global memory), then count the warp in.
-__device__ __forceinline__ void ln_signal_block_done(uint32_t counter_smem, int lane) {
+// A warp's rows of a row block are written: make them visible to the TMA loads that will read them (generic-proxy
+// stores, async-proxy loads of the same global memory), then publish the warp's progress.
+//   add != 0: add 1 to the word (the epilogue warps' shared arrival count for the worker's first block)
+//   add == 0: store `value` (a LayerNorm warp's own count of finished blocks)
+__device__ __forceinline__ void ln_publish(uint32_t word_smem, int lane, int add, uint32_t value) {
   __threadfence();                                          // every lane's rows are in L2 ...
   asm volatile("fence.proxy.async.global;" ::: "memory");   // ... and ordered before async-proxy reads of them
   __syncwarp();
-  if (lane == 0) asm volatile("red.release.gpu.shared::cta.add.u32 [%0], 1;" ::"r"(counter_smem) : "memory");
+  if (lane == 0) {
+    if (add) asm volatile("red.release.gpu.shared::cta.add.u32 [%0], 1;" ::"r"(word_smem) : "memory");
+    else asm volatile("st.release.gpu.shared::cta.u32 [%0], %1;" ::"r"(word_smem), "r"(value) : "memory");
+  }
 }
-// Bounded wait of the TMA producer for the counter to reach `target`.
-__device__ __forceinline__ bool ln_wait_blocks(uint32_t counter_smem, uint32_t target) {
-  for (int i = 0; i < (1 << 23); ++i) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(counter_smem) : "memory");
-    if (v >= target) {
+// Bounded wait of the TMA producer until the epilogue warps have all counted in (first block) and every LayerNorm
+// warp has finished `blocks` row blocks. Each warp publishes only its own progress, so a warp that runs ahead
+// cannot stand in for one that is behind.
+__device__ __forceinline__ bool ln_wait_blocks(uint32_t words_smem, uint32_t blocks) {
+  unsigned long long t0 = 0;
+  for (int i = 0;; ++i) {
+    uint32_t v, lo = 0xffffffffu;
+    asm volatile("ld.acquire.gpu.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(words_smem) : "memory");
+    bool ok = v >= uint32_t(kEpiWarps);
+#pragma unroll
+    for (int w = 0; w < kLnWarps; ++w) {
+      asm volatile("ld.acquire.gpu.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(words_smem + 16u + 4u * w) : "memory");
+      lo = v < lo ? v : lo;
+    }
+    if (ok && lo >= blocks) {
       asm volatile("fence.proxy.async.global;" ::: "memory");
       return true;
     }
-    if (i > 2048) __nanosleep(64);
+    if (i == 64) t0 = global_timer_ns();
+    if (i > 64) {
+      __nanosleep(100);
+      if (global_timer_ns() - t0 > 2000000000ull) return false;
+    }
   }
-  return false;
 }
 
 template <int BN, int KIND, int PAIR, int RES, int O8, int LNA>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads + (LNA ? 32 * kLnWarps : 0), 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
   using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA>;
@@ -315,7 +348,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto tile_of = [&](int i, int& mi, int& ni) -> bool {
     if constexpr (LNA) {
       mi = worker + (i / tiles_n) * num_workers;
-      ni = i % tiles_n;
+      ni = (i % tiles_n + worker) % tiles_n;      // staggered: the workers do not all want the same W tile at once
       return mi < tiles_m;
     } else {
       const int t = worker + i * num_workers;
@@ -334,7 +367,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(empty_bar(s), 1);
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(base + Cfg::RBAR_OFF + 8u * w, 1);
-    asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(ln_counter), "r"(0u) : "memory");
+    for (int w = 0; w < 12; ++w) asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(ln_counter + 4u * w), "r"(0u) : "memory");
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
@@ -344,6 +377,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) {
     tmem_alloc<PAIR>(smem_u32(tmem_slot), Cfg::ACC_COLS);
     tmem_relinquish<PAIR>();
+  }
+  if constexpr (LNA) {
+    // LayerNorm weight and bias (f16) into shared memory: every row needs them, and from global memory they would
+    // put a second round trip behind each row's own loads
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      const bool in = i % 128 * 8 < p.K;
+      const __half* src = (i < 128 ? p.ln_w16 : p.ln_b16) + i % 128 * 8;
+      const uint4 u = in ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0u, 0u, 0u, 0u);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + Cfg::LN_PRM_OFF + 16u * i), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w) : "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -362,9 +405,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = mi * TM + rank * BM;                  // this CTA's rows of A
         const int n0 = ni * BN + rank * (PAIR ? BN / 2 : 0);  // this CTA's rows of W
         if constexpr (LNA) {
-          // the first tile of a row block waits until this CTA's 128 rows of it are normalised: every epilogue warp
-          // counts in once per block, and no warp starts on block j + 1 before block j's tiles run
-          if (ni == 0 && !ln_wait_blocks(ln_counter, uint32_t(kEpiWarps * (i / tiles_n + 1)))) {
+          // the first tile of a row block waits until this CTA's 128 rows of it are normalised
+          if (i % tiles_n == 0 && !ln_wait_blocks(ln_counter, uint32_t(i / tiles_n + 1))) {
             atomicCAS(p.status, 0, kDevTimeoutProducer);
             ok = false;
             break;
@@ -381,14 +423,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (PAIR) {
             // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
             const uint32_t lead_full = mapa_u32(full_bar(s), 0);
-#ifdef CRL_EXP_SKIP_A
-            const bool skip_a = LNA != 0 && ni > 0;     // timing experiment only: wrong results
-            if (rank == 0) mbar_expect_tx(full_bar(s), skip_a ? 2 * Cfg::B_BYTES : 2 * Cfg::STAGE_BYTES);
-            if (!skip_a) tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, lead_full);
-#else
             if (rank == 0) mbar_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
             tma_load_2d_pair(a_dst, &tmA, kb * BK, m0, lead_full);
-#endif
             tma_load_2d_pair(b_dst, &tmB, kb * BK, n0, lead_full);
           } else {
             mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
@@ -441,6 +477,25 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     __syncwarp();
+  } else if (LNA != 0 && warp >= 2 + kEpiWarps) {
+    // ------------------------------------------------------------------ LayerNorm warps (LNA kernels)
+    // This CTA's 128 rows of every row block of the worker, block after block, normalised into x / x8 ahead of
+    // the TMA producer (which waits for a block's rows before it loads the block's first tile). The worker's
+    // first block is shared with the epilogue warps, which have nothing to drain yet; the rows of the block
+    // after the one in work are requested into L2 while it is normalised.
+    const int lw = warp - 2 - kEpiWarps;
+    const uint32_t prm = base + Cfg::LN_PRM_OFF;
+    if (worker < tiles_m && lane < 3)      // the warp's first rows, before anything else
+      ln_prefetch_row(p, (long long)worker * TM + rank * BM + kEpiWarps + lw + (long long)lane * (kEpiWarps + kLnWarps));
+    for (int j = 0;; ++j) {
+      const int mi = worker + j * num_workers;
+      if (mi >= tiles_m) break;
+      const long long row0 = (long long)mi * TM + rank * BM;
+      const long long next_first = (mi + num_workers < tiles_m) ? row0 + (long long)num_workers * TM + lw : -1;
+      if (j == 0) ln_rows_of_block(p, prm, row0, BM, kEpiWarps + lw, kEpiWarps + kLnWarps, lane, next_first, kLnWarps);
+      else ln_rows_of_block(p, prm, row0, BM, lw, kLnWarps, lane, next_first, kLnWarps);
+      ln_publish(ln_counter + 16u + 4u * lw, lane, 0, uint32_t(j + 1));
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int ew = warp - 2;                // 0..15
@@ -478,43 +533,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool tma_res = RES != 0 && p.use_tma_res != 0 && p.residual != nullptr;
       if (RES != 0 && tma_res && res_wanted(0)) res_issue(0);
       const bool mish8 = O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0;
-      // LNA: the epilogue warps are idle most of a tile, so they also normalise the rows of A. Warp ew owns rows ew,
-      // ew + 16, ... (8 of this CTA's 128) of every row block: all of the worker's first block up front, then a
-      // slice of the NEXT block after each tile's store, finished well before the producer needs that block.
-      constexpr int kRowsPerWarp = BM / kEpiWarps;
-      const int ln_per_tile = (kRowsPerWarp + tiles_n - 1) / tiles_n;
       if constexpr (LNA) {
+        // the worker's first row block: nothing to drain yet, so the epilogue warps normalise rows too
         if (worker < tiles_m) {
-          ln_prefetch_rows(p, (long long)worker * TM + rank * BM, BM, ew, kEpiWarps, lane, 0, kRowsPerWarp);
-          if (worker + num_workers < tiles_m)     // the first slice of the second block, normalised after the first tile
-            ln_prefetch_rows(p, (long long)(worker + num_workers) * TM + rank * BM, BM, ew, kEpiWarps, lane, 0, ln_per_tile);
-          ln_rows_of_block(p, (long long)worker * TM + rank * BM, BM, ew, kEpiWarps, lane);
+          const long long row0 = (long long)worker * TM + rank * BM;
+          if (lane < 3) ln_prefetch_row(p, row0 + ew + (long long)lane * (kEpiWarps + kLnWarps));
+          ln_rows_of_block(p, base + Cfg::LN_PRM_OFF, row0, BM, ew, kEpiWarps + kLnWarps, lane);
         }
-        ln_signal_block_done(ln_counter, lane);
+        ln_publish(ln_counter, lane, 1, 0u);
       }
-      // at the start of a tile: prefetch the slice that will be normalised after the NEXT tile
-      auto ln_prefetch_ahead = [&](int cur_mi, int cur_ni) {
-        if constexpr (LNA) {
-          int nni = cur_ni + 1, nmi = cur_mi + num_workers;      // the slice after tile (cur_mi, cur_ni + 1) belongs to block nmi
-          if (nni >= tiles_n) { nni = 0; nmi += num_workers; }   // ... or, after this block's last tile, to the block after
-          const int j0 = nni * ln_per_tile;
-          if (j0 < kRowsPerWarp && nmi < tiles_m) {
-            const int cnt = (j0 + ln_per_tile <= kRowsPerWarp) ? ln_per_tile : kRowsPerWarp - j0;
-            ln_prefetch_rows(p, (long long)nmi * TM + rank * BM, BM, ew, kEpiWarps, lane, j0, cnt);
-          }
-        }
-      };
-      auto ln_step = [&](int cur_mi, int cur_ni) {
-        if constexpr (LNA) {
-          const int j0 = cur_ni * ln_per_tile;
-          const int nmi = cur_mi + num_workers;
-          if (j0 < kRowsPerWarp && nmi < tiles_m) {
-            const int cnt = (j0 + ln_per_tile <= kRowsPerWarp) ? ln_per_tile : kRowsPerWarp - j0;
-            ln_rows_of_block(p, (long long)nmi * TM + rank * BM, BM, ew, kEpiWarps, lane, j0, cnt);
-            if (j0 + cnt == kRowsPerWarp) ln_signal_block_done(ln_counter, lane);
-          }
-        }
-      };
       bool alive = true;
       int local = 0;
       int mi = 0, ni = 0;
@@ -523,21 +550,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t aph = (local >> 1) & 1u;
         const int m0 = mi * TM + rank * BM;   // first row of this CTA's accumulator half
         const int n0 = ni * BN;
-        // this tile's bias slice goes to shared memory while the MMAs are still running
-        if (p.bias != nullptr) {
-          for (int e = et; e < BN; e += kEpiWarps * 32) bias_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.0f;
-        }
-        if constexpr (KIND == kKindI8) {
-          if (p.col_scale != nullptr)
-            for (int e = et; e < BN; e += kEpiWarps * 32) cs_s[as * BN + e] = (n0 + e < p.N) ? __ldg(p.col_scale + n0 + e) : 0.0f;
-        }
-        asm volatile("bar.sync 1, 512;" ::: "memory");   // epilogue warps only; also orders reuse of bias_s
-        ln_prefetch_ahead(mi, ni);
-        if (alive && !mbar_wait(tfull_bar(as), aph)) {
+        // (no barrier among the epilogue warps anywhere in this loop: a warp that is late - a residual slab or a
+        // LayerNorm row still on its way - must not keep the others from draining the next accumulator)
+        if (!mbar_wait(tfull_bar(as), aph)) {
           if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
-          alive = false;           // keep iterating so that the named barrier above stays balanced
+          alive = false;
+          break;
         }
-        if (!alive) continue;
         tc_fence_after();
         const int c0 = n0 + part * 64;
         const bool active = c0 < p.N;       // warp-uniform
@@ -553,7 +572,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) bulk_wait_read0();
             res_issue(local + 1);
           }
-          ln_step(mi, ni);
           continue;
         }
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(as * BN + part * 64);
@@ -561,13 +579,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const bool row_ok = row < p.M;
         const int rrow = p.res_mod > 0 ? row % p.res_mod : row;
         const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-        const float a_scale = p.alpha * rs;
+        // e4m3 output without an activation or residual: out = (alpha acc + bias) s = (alpha s) acc + (bias s), one
+        // multiply-add per element instead of three operations
+        const bool fold = O8 != 0 && p.act == kActNone && p.residual == nullptr;
+        const float os = fold ? 1.0f : p.out_scale;
+        const float bs = fold ? p.out_scale : 1.0f;
+        const float a_scale = p.alpha * rs * bs;
         // the slab buffer: the residual slab has landed in it (RES), or the previous tile's store has read it
         if (RES != 0 && tma_res) {
           if (!mbar_wait(rbar, rph)) {
             if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
             alive = false;
-            continue;
+            break;
           }
           rph ^= 1u;
           res_pending = false;
@@ -576,6 +599,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           __syncwarp();
         }
         const bool direct_res = p.residual != nullptr && !(RES != 0 && tma_res) && row_ok;
+        // bias and per-column scales: 16 floats per piece, the same addresses for every lane (one L1 transaction each)
+        const bool tab_vec = c0 + 64 <= p.N && (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+                             (p.col_scale == nullptr || (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
         const bool res_vec = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
         // two TMEM loads of 32 columns, each waited for before anything else touches its registers (a tcgen05.ld
         // fills them asynchronously); each half is then worked on as two pieces of 16 columns
@@ -603,20 +629,31 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if constexpr (KIND == kKindI8) {
             if (p.col_scale != nullptr) {
-              const float4* c4p = reinterpret_cast<const float4*>(cs_s + as * BN + part * 64 + i * 16);
+              if (tab_vec) {
+                const float4* c4p = reinterpret_cast<const float4*>(p.col_scale + c0 + i * 16);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float4 c4 = c4p[q];
-                v[q * 4] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+                for (int q = 0; q < 4; ++q) {
+                  const float4 c4 = __ldg(c4p + q);
+                  v[q * 4] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= (c0 + i * 16 + j < p.N) ? __ldg(p.col_scale + c0 + i * 16 + j) : 0.0f;
               }
             }
           }
           if (p.bias != nullptr) {
-            const float4* b4p = reinterpret_cast<const float4*>(bias_s + as * BN + part * 64 + i * 16);
+            if (tab_vec) {
+              const float4* b4p = reinterpret_cast<const float4*>(p.bias + c0 + i * 16);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 b4 = b4p[q];
-              v[q * 4] += b4.x; v[q * 4 + 1] += b4.y; v[q * 4 + 2] += b4.z; v[q * 4 + 3] += b4.w;
+              for (int q = 0; q < 4; ++q) {
+                const float4 b4 = __ldg(b4p + q);
+                v[q * 4] = fmaf(b4.x, bs, v[q * 4]); v[q * 4 + 1] = fmaf(b4.y, bs, v[q * 4 + 1]);
+                v[q * 4 + 2] = fmaf(b4.z, bs, v[q * 4 + 2]); v[q * 4 + 3] = fmaf(b4.w, bs, v[q * 4 + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = fmaf((c0 + i * 16 + j < p.N) ? __ldg(p.bias + c0 + i * 16 + j) : 0.0f, bs, v[j]);
             }
           }
           // activation: the switch sits outside the element loop so that the independent evaluations interleave;
@@ -650,8 +687,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const __half2 z1 = __hmul2(*reinterpret_cast<const __half2*>(&y1), s2);
                 w[j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&z0), __NV_SATFINITE, __NV_E4M3)) |
                        (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&z1), __NV_SATFINITE, __NV_E4M3)) << 16);
+              } else if (fold) {
+                w[j] = uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[0], e[1]), __NV_SATFINITE, __NV_E4M3)) |
+                       (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[2], e[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
               } else {
-                const float os = p.out_scale;
                 w[j] = uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[0] * os, e[1] * os), __NV_SATFINITE, __NV_E4M3)) |
                        (uint32_t(__nv_cvt_float2_to_fp8x2(make_float2(e[2] * os, e[3] * os), __NV_SATFINITE, __NV_E4M3)) << 16);
               }
@@ -704,7 +743,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_store_2d(&tmC, slot, c0, m0 + quarter * 32);
           bulk_commit();
         }
-        ln_step(mi, ni);
         if (RES != 0 && tma_res) {
           if (res_wanted(local + 1)) {
             if (lane == 0) bulk_wait_read0();   // the store above has read the buffer: the next residual slab may land

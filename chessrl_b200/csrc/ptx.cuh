@@ -45,27 +45,38 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+  // The last operand is the suspend-time hint: the thread may sleep inside the instruction until the phase
+  // completes (it is woken then) or the hint runs out, instead of returning at once and spinning through issue
+  // slots the working warps of the SM need.
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(0x989680u)
       : "memory");
   return ok;
 }
-// Bounded wait: a few thousand hot polls, then polls with a short sleep. Gives up after roughly
-// a second and returns false.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: every try may sleep inside the instruction; the wall-clock bound (two seconds on the GPU's
+// nanosecond timer) is what ends a wait that can never succeed, however long or short the hardware lets a
+// single try sleep. Returns false when it gives up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  for (int i = 0; i < (1 << 22); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(128);
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+    // the clock is looked at once per 256 tries only: the loop around a failed try stays three instructions
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > 2000000000ull) return false;
   }
-  return false;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -211,10 +211,11 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
   }
 }
 
-// The per-layer LayerNorms (no gating, no int8): persistent warps walk rows grid-stride with the affine
+// The per-layer LayerNorms (no gating): persistent warps walk rows grid-stride with the affine
 // parameters of their own columns held in registers as f16 pairs. The plain kernel above re-reads weight and
 // bias through L1 for every row (four times the bytes of the row itself), which made L1 throughput, not HBM,
 // its limit; here a row costs one 16-byte load and at most two stores per lane and vector.
+template <bool Q8>      // Q8: also emit per-token int8 rows (the W8A8 engine)
 __global__ void __launch_bounds__(256) ln_rows_persistent_kernel(const LnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int NV = 4;
@@ -241,6 +242,7 @@ __global__ void __launch_bounds__(256) ln_rows_persistent_kernel(const LnParams 
     raw[i] = c < p.d ? *reinterpret_cast<const uint4*>(p.x + row * p.ldx + c) : make_uint4(0u, 0u, 0u, 0u);
   }
   const __half2 s8 = __floats2half2_rn(p.out8_scale, p.out8_scale);
+  uint32_t yrow[Q8 ? NV : 1][4];      // the normalised row as f16 pairs (int8 output only)
   for (; row < p.rows; row += stride) {
     const long long nrow = row + stride;
 #pragma unroll
@@ -291,6 +293,41 @@ __global__ void __launch_bounds__(256) ln_rows_persistent_kernel(const LnParams 
                     (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
           }
           *reinterpret_cast<uint2*>(p.y8 + row * p.ldy8 + c) = make_uint2(w8[0], w8[1]);
+        }
+        if constexpr (Q8) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) yrow[i][j] = o16[j];       // kept for the per-token int8 pass below
+        }
+      }
+    }
+    if constexpr (Q8) {
+      // dynamic per-token int8 (W8A8): row maximum of |y| over the normalised values still in registers
+      __half2 m2 = __float2half2_rn(0.0f);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        if ((i * 32 + lane) * 8 < p.d) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __half2*>(&yrow[i][j])));
+        }
+      }
+      float amax = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+      const float qinv = 1.0f / sc;
+      if (lane == 0) p.yq_scale[row] = sc;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 8;
+        if (c < p.d) {
+          __align__(8) signed char q8[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yrow[i][j]));
+            q8[2 * j] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.x * qinv))));
+            q8[2 * j + 1] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.y * qinv))));
+          }
+          *reinterpret_cast<uint2*>(p.yq + row * p.d + c) = *reinterpret_cast<const uint2*>(q8);
         }
       }
     }
@@ -392,40 +429,49 @@ __global__ void __launch_bounds__(256) bias_correct_kernel(const __half* __restr
   if (lane == 0) out[n] = bias[n] + acc;
 }
 
-// f16 rows -> per-row symmetric int8 + scale (dynamic per-token activation quantisation); one warp per row,
-// cols a multiple of 8.
+// f16 rows -> per-row symmetric int8 + scale (dynamic per-token activation quantisation); one warp per row, the row
+// read once and held in registers (cols a multiple of 8, at most 4096).
 __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const __half* __restrict__ x, long long rows, int cols,
                                                             int8_t* __restrict__ q, float* __restrict__ scale) {
+  constexpr int NV = 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 8 + warp;
-  if (row >= rows) return;
-  const __half* xr = x + row * cols;
-  float amax = 0.0f;
-  for (int c = lane * 8; c < cols; c += 256) {
-    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);
-    const __half2* h = reinterpret_cast<const __half2*>(&u);
+  const long long stride = (long long)gridDim.x * 8;
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < rows; row += stride) {
+    const __half* xr = x + row * cols;
+    uint4 raw[NV];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h[j]);
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      raw[i] = c < cols ? *reinterpret_cast<const uint4*>(xr + c) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
+    __half2 m2 = __float2half2_rn(0.0f);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
-  const float inv = 1.0f / sc;
-  if (lane == 0) scale[row] = sc;
-  for (int c = lane * 8; c < cols; c += 256) {
-    const uint4 u = *reinterpret_cast<const uint4*>(xr + c);   // second read hits L1/L2
-    const __half2* h = reinterpret_cast<const __half2*>(&u);
-    __align__(8) signed char q8[8];
+    for (int i = 0; i < NV; ++i) {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __half22float2(h[j]);
-      q8[2 * j] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.x * inv))));
-      q8[2 * j + 1] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.y * inv))));
+      for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(h[j]));
     }
-    *reinterpret_cast<uint2*>(q + row * cols + c) = *reinterpret_cast<const uint2*>(q8);
+    float amax = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = amax > 0.0f ? amax / 127.0f : 1.0f;
+    const float inv = 1.0f / sc;
+    if (lane == 0) scale[row] = sc;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < cols) {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+        __align__(8) signed char q8[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          q8[2 * j] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.x * inv))));
+          q8[2 * j + 1] = static_cast<signed char>(max(-127, min(127, __float2int_rn(f.y * inv))));
+        }
+        *reinterpret_cast<uint2*>(q + row * cols + c) = *reinterpret_cast<const uint2*>(q8);
+      }
+    }
   }
 }
 

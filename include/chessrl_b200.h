@@ -84,12 +84,13 @@ typedef struct crl_config {
   int32_t chunk;            /* positions processed per pass over the layers; 0 = library default */
   int32_t pos_embed;        /* 1: add the `pe` table [>=64, d] to the embedded tokens (model_bis.py:363-366) */
   int32_t lm_vocab;         /* CRL_POLICY_LM_HEAD: rows of lm_head.weight (1929 in the reference's scripts) */
-  int32_t fuse_layernorm;   /* CRL_FUSE_LN_AUTO (0): large passes of post-LN networks run the per-block LayerNorms inside
-                               the ff1 / QKV GEMM kernels; CRL_FUSE_LN_OFF: always as separate row passes */
+  int32_t fuse_layernorm;   /* CRL_FUSE_LN_OFF (0): the per-block LayerNorms are separate row passes; CRL_FUSE_LN_ON: large
+                               passes of post-LN networks run them inside the ff1 / QKV GEMM kernels (same bits; measured
+                               neither faster nor slower on B200, kept as an option) */
   int32_t precision;        /* bit mask of CRL_PREC_*; 0 = the fastest arithmetic of the chosen dtype */
 } crl_config;
 
-enum { CRL_FUSE_LN_AUTO = 0, CRL_FUSE_LN_OFF = 1 };
+enum { CRL_FUSE_LN_OFF = 0, CRL_FUSE_LN_ON = 1 };
 /* Precision switches. The FP8 engine (model_fp8.py:43-140: per-tensor e4m3 linears, everything else in higher
  * precision) takes several shortcuts around its e4m3 GEMMs by default; each bit takes one of them back, so that its
  * cost in accuracy and speed can be measured on its own:

@@ -486,6 +486,38 @@ def test_value_driven_move_selection_matches_oracle():
         model.get_best_move_value("1n1Rkb1r/p4ppp/4q3/4p1B1/4P3/8/PPP2PPP/2K5 b k - 1 17")
 
 
+@pytest.mark.parametrize("gain", [8.0, 32.0])
+def test_large_attention_scores_stay_finite_and_bounded(gain):
+    """The fast attention kernels accumulate Q K^T in f16 and run the softmax on packed f16. With the query / key
+    projections scaled up (raw scores in the tens to hundreds instead of O(1), as a trained network may have)
+    nothing may overflow to inf / NaN, and the fp32-score kernel (CRL_PREC_ATTN_F32) must stay inside the FP16
+    tolerance; the fast kernel's own error is printed and bounded at the looser figure it shows here."""
+    from chessrl_b200 import Engine, EngineConfig
+    import chessrl_b200 as crl
+    cfg = bt4spec.SpecConfig.baseline(2, 256, 512, 8, smolgen=True)
+    spec = bt4spec.BT4Spec(cfg)
+    sd = bt4spec.seeded_state_dict(spec, seed=61)
+    for l in range(2):
+        for name in ("query_proj", "key_proj"):
+            sd[f"layers.{l}.attention.{name}.weight"] = sd[f"layers.{l}.attention.{name}.weight"] * gain
+    tokens = random_tokens(6, cfg.planes, seed=62)
+    ref = oracle_out(cfg, sd, tokens)
+    x = tokens.view(6, 8, 8, -1).cuda()
+    errs = {}
+    for label, prec in (("fast", 0), ("fp32 scores", crl.PREC_ATTN_F32)):
+        eng = Engine(EngineConfig(dtype=0, precision=prec, **cfg.to_dict()))
+        eng.load_state_dict(sd)
+        out = eng.forward(x, wdl_softmax=True)
+        torch.cuda.synchronize()
+        pol, wdl = out["policy"].float().cpu(), out["wdl"].cpu()
+        assert torch.isfinite(pol).all() and torch.isfinite(wdl).all(), label
+        errs[label] = ((pol - ref["policy"]).abs().max().item(), (wdl - torch.softmax(ref["wdl"], -1)).abs().max().item())
+        eng.close()
+    print(f"Q/K weights x{gain}: policy / wdl max-abs error fast {errs['fast']}, fp32 scores {errs['fp32 scores']}")
+    assert errs["fp32 scores"][0] <= POLICY_TOL and errs["fp32 scores"][1] <= WDL_TOL
+    assert errs["fast"][0] <= 5 * POLICY_TOL and errs["fast"][1] <= 5 * WDL_TOL
+
+
 FENS = ["r3k2r/p1ppqpb1/bn2pnp1/3PN3/1p2P3/2N2Q1p/PPPBBPPP/R3K2R w KQkq - 0 1",
         "rnbqkbnr/ppp1pppp/8/8/3pP3/8/PPPP1PPP/RNBQKBNR b KQkq e3 0 2",
         "8/P7/8/8/8/8/k6p/4K3 w - - 0 1", "8/P7/8/8/8/8/k6p/4K3 b - - 0 1"]
@@ -623,8 +655,9 @@ def test_q_value_entry_points_and_many_position_scoring():
 
 @pytest.mark.parametrize("dtype", [0, 1])
 def test_gemm_fused_layernorm_equals_separate_passes(dtype):
-    """Large passes of post-LN networks normalise inside the ff1 / QKV GEMM kernels. The fused warps use the
-    arithmetic of the stand-alone LayerNorm kernel, so switching the fusion off must not change a single bit."""
+    """With crl_config.fuse_layernorm on, large passes of post-LN networks normalise inside the ff1 / QKV GEMM
+    kernels. The fused warps use the arithmetic of the stand-alone LayerNorm kernel, so switching the fusion on
+    must not change a single bit."""
     from chessrl_b200 import Engine, EngineConfig, positions
     import chessrl_b200 as crl
     cfg = bt4spec.SpecConfig.baseline(3, 256, 512, 8, smolgen=True)
@@ -634,7 +667,7 @@ def test_gemm_fused_layernorm_equals_separate_passes(dtype):
     pos = positions.playout_positions(b, seed=21)
     planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
     outs = []
-    for fuse in (crl.FUSE_LN_AUTO, crl.FUSE_LN_OFF):
+    for fuse in (crl.FUSE_LN_ON, crl.FUSE_LN_OFF):
         eng = Engine(EngineConfig(dtype=dtype, fuse_layernorm=fuse, **cfg.to_dict()))
         eng.load_state_dict(sd)
         if dtype == crl.DTYPE_F8E4M3:
