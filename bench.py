@@ -527,12 +527,12 @@ def main():
         peak, peak_note = peaks["bf16_tflops"], f"bf16_tflops, {peak_kind}"
     gm = prof["gemm"]
     achieved = top[2] / (top[1] * 1e-3) / 1e12 if top[1] > 0 else 0.0
-    # DRAM bytes per launch from a profiler capture of this kernel and shape: 137.6 MB read + 355.5 MB written at
-    # M = 131072, N = 3072, K = 1024, e4m3 in and out (47 MB of the 402.7 MB output were still in L2 when the kernel
+    # DRAM bytes per launch from a profiler capture of this kernel and shape: 137.5 MB read + 351.6 MB written at
+    # M = 131072, N = 3072, K = 1024, e4m3 in and out (51 MB of the 402.7 MB output were still in L2 when the kernel
     # ended); A and C grow in proportion to M, so the figure is scaled by the rows of the timed launch
     traffic = None
     if top_shape[1:] == (3072, 1024, 1):
-        traffic = int(493.1e6 * top_shape[0] / 131072)
+        traffic = int(489.1e6 * top_shape[0] / 131072)
     all_gemm = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
     roofline = {"bound": "tensor",
                 "kernel": "gemm_tn_kernel<256,%s,pair> M=%d N=%d K=%d (the GEMM shape with the largest share of the pass)"

@@ -391,7 +391,12 @@ int quant_rows_i8(crl_handle* h, const __half* x, long long rows, int cols, uint
   if (cols > 4096 || cols % 8 != 0) return fail(h, CRL_ERR_SHAPE, "per-token int8 rows are at most 4096 wide");
   const long long want = (rows + 7) / 8;
   const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 8));
-  quant_rows_i8_kernel<<<grid, 256, 0, s>>>(x, rows, cols, reinterpret_cast<int8_t*>(q), scale);
+  int8_t* q8 = reinterpret_cast<int8_t*>(q);
+  // the row sits in registers: the narrowest instantiation that holds it keeps the most warps resident
+  if (cols <= 1024) quant_rows_i8_kernel<4><<<grid, 256, 0, s>>>(x, rows, cols, q8, scale);
+  else if (cols <= 1536) quant_rows_i8_kernel<6><<<grid, 256, 0, s>>>(x, rows, cols, q8, scale);
+  else if (cols <= 2048) quant_rows_i8_kernel<8><<<grid, 256, 0, s>>>(x, rows, cols, q8, scale);
+  else quant_rows_i8_kernel<16><<<grid, 256, 0, s>>>(x, rows, cols, q8, scale);
   CRL_CUDA(h, cudaGetLastError());
   ++h->launches;
   return CRL_OK;

@@ -622,10 +622,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
           float v[16];
+          float sc[16];      // per-element multiplier of the raw accumulator: alpha, row scale (and column scale)
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            if constexpr (KIND == kKindI8) v[j] = static_cast<float>(static_cast<int>(acc[(i & 1) * 16 + j])) * a_scale;
-            else v[j] = __uint_as_float(acc[(i & 1) * 16 + j]) * a_scale;
+            if constexpr (KIND == kKindI8) v[j] = static_cast<float>(static_cast<int>(acc[(i & 1) * 16 + j]));
+            else v[j] = __uint_as_float(acc[(i & 1) * 16 + j]);
+            sc[j] = a_scale;
           }
           if constexpr (KIND == kKindI8) {
             if (p.col_scale != nullptr) {
@@ -634,27 +636,38 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                   const float4 c4 = __ldg(c4p + q);
-                  v[q * 4] *= c4.x; v[q * 4 + 1] *= c4.y; v[q * 4 + 2] *= c4.z; v[q * 4 + 3] *= c4.w;
+                  sc[q * 4] *= c4.x; sc[q * 4 + 1] *= c4.y; sc[q * 4 + 2] *= c4.z; sc[q * 4 + 3] *= c4.w;
                 }
               } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] *= (c0 + i * 16 + j < p.N) ? __ldg(p.col_scale + c0 + i * 16 + j) : 0.0f;
+                for (int j = 0; j < 16; ++j) sc[j] *= (c0 + i * 16 + j < p.N) ? __ldg(p.col_scale + c0 + i * 16 + j) : 0.0f;
               }
             }
           }
+          // v = raw * sc + bias * bs: one multiply-add per element when bs is 1 (no folded output scale)
+          float bv[16];
           if (p.bias != nullptr) {
             if (tab_vec) {
               const float4* b4p = reinterpret_cast<const float4*>(p.bias + c0 + i * 16);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const float4 b4 = __ldg(b4p + q);
-                v[q * 4] = fmaf(b4.x, bs, v[q * 4]); v[q * 4 + 1] = fmaf(b4.y, bs, v[q * 4 + 1]);
-                v[q * 4 + 2] = fmaf(b4.z, bs, v[q * 4 + 2]); v[q * 4 + 3] = fmaf(b4.w, bs, v[q * 4 + 3]);
+                bv[q * 4] = b4.x; bv[q * 4 + 1] = b4.y; bv[q * 4 + 2] = b4.z; bv[q * 4 + 3] = b4.w;
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = fmaf((c0 + i * 16 + j < p.N) ? __ldg(p.bias + c0 + i * 16 + j) : 0.0f, bs, v[j]);
+              for (int j = 0; j < 16; ++j) bv[j] = (c0 + i * 16 + j < p.N) ? __ldg(p.bias + c0 + i * 16 + j) : 0.0f;
             }
+            if (fold) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = fmaf(v[j], sc[j], bv[j] * bs);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = fmaf(v[j], sc[j], bv[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= sc[j];
           }
           // activation: the switch sits outside the element loop so that the independent evaluations interleave;
           // Mish into an e4m3 output runs on packed f16 pairs at the conversion below

@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
 // bias through L1 for every row (four times the bytes of the row itself), which made L1 throughput, not HBM,
 // its limit; here a row costs one 16-byte load and at most two stores per lane and vector.
 template <bool Q8>      // Q8: also emit per-token int8 rows (the W8A8 engine)
-__global__ void __launch_bounds__(256) ln_rows_persistent_kernel(const LnParams p) {
+__global__ void __launch_bounds__(256, 2) ln_rows_persistent_kernel(const LnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int NV = 4;
   const long long stride = (long long)gridDim.x * 8;
@@ -431,9 +431,9 @@ __global__ void __launch_bounds__(256) bias_correct_kernel(const __half* __restr
 
 // f16 rows -> per-row symmetric int8 + scale (dynamic per-token activation quantisation); one warp per row, the row
 // read once and held in registers (cols a multiple of 8, at most 4096).
+template <int NV>       // NV x 256 columns at most
 __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const __half* __restrict__ x, long long rows, int cols,
                                                             int8_t* __restrict__ q, float* __restrict__ scale) {
-  constexpr int NV = 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long stride = (long long)gridDim.x * 8;
   for (long long row = (long long)blockIdx.x * 8 + warp; row < rows; row += stride) {
