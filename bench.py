@@ -14,11 +14,12 @@ PyTorch on CPU and is not on this machine) on the host cores, on a bounded sampl
 Small repeatable programs for a profiler capture (`-k regex:<kernel>`); they print timings, not the JSON line:
     python bench.py --case gemm <kind> <M> <N> <K> <out> [act] [residual]
         one linear layer through `crl_linear` (kind: 0 f16, 1 e4m3, 2 int8 operands; out: 0 f16, 1 f32, 2 e4m3):
-        three launches, then 20 more timed with CUDA events
+        three launches, then 20 more timed with CUDA events (residual 1: + f16 residual; 2: + residual and the
+        LayerNorm of the output rows inside the kernel, in place, with an e4m3 copy, through `crl_linear_ex`)
     python bench.py --case forward <f16|f8|i8> <positions> [chunk [fuse_layernorm [precision]]]
         the BT4-shaped forward pass: plain timing of three passes, then one pass with the library's per-launch
         CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm 1 = LayerNorms inside the
-        ff1 / QKV GEMM kernels; precision = CRL_PREC_* bit mask)
+        ff1 / QKV GEMM kernels, 2 = inside the out-projection / ff2 kernels; precision = CRL_PREC_* bit mask)
 """
 import argparse
 import json
@@ -294,6 +295,27 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
     def launch():
         return lib.crl_linear(kind, a.data_ptr(), K, w.data_ptr(), K, c.data_ptr(), N, out, M, N, K, b.data_ptr(),
                               r.data_ptr() if r is not None else None, N, 0.01, act, status.data_ptr(), None)
+
+    if residual == 2:
+        # res = 2: the rows are normalised inside the kernel (LayerNorm of acc + bias + residual), written over the
+        # residual, with an e4m3 copy: the out-projection / ff2 kernels of CRL_FUSE_LN_OUT
+        import ctypes
+        gamma = torch.ones(N, device=dev, dtype=torch.float16)
+        beta = torch.zeros(N, device=dev, dtype=torch.float16)
+        x8 = torch.empty(M, N, device=dev, dtype=torch.uint8)
+        scratch = torch.zeros(256 * ((M + 255) // 256) * ((N + 255) // 256), device=dev, dtype=torch.int64)
+        x = _lib.LinearArgs()
+        x.kind, x.out_dtype = kind, 0
+        x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), K, w.data_ptr(), K, r.data_ptr(), N
+        x.m, x.n, x.k = M, N, K
+        x.bias, x.residual, x.ldr = b.data_ptr(), r.data_ptr(), N
+        x.alpha, x.act, x.out_scale = 0.01, act, 1.0
+        x.device_status = status.data_ptr()
+        x.lno_weight, x.lno_bias, x.lno_scratch = gamma.data_ptr(), beta.data_ptr(), scratch.data_ptr()
+        x.lno_x8, x.lno_out8_scale = x8.data_ptr(), 64.0
+
+        def launch():
+            return lib.crl_linear_ex(ctypes.byref(x))
 
     for _ in range(3):
         rc = launch()

@@ -251,6 +251,7 @@ struct Workspace {
   float* logits;    // [bc, 1929] f32 (dense form)
   __half *v2, *v2q;
   uint8_t* legal;      // [batch, 236] legal-move bitsets generated from the packed records
+  unsigned long long* lno_stats;   // exchange buffer of the GEMM kernels that normalise their output rows
   size_t total;
 };
 
@@ -300,6 +301,9 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc, int64_t total) {
   w.v2 = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(total) * 236 : 0));
+  // one 8-byte record per row and 256-column tile, rows rounded up to whole 256-row blocks
+  const bool lno = c.fuse_layernorm == CRL_FUSE_LN_OUT && c.ln_mode == CRL_LN_POST && c.dtype != CRL_DTYPE_I8 && d % 256 == 0;
+  w.lno_stats = reinterpret_cast<unsigned long long*>(take(lno ? align_up(M, 256) * (d / 256) * 8 : 0));
   w.total = off;
   return w;
 }
@@ -338,6 +342,10 @@ struct Lin {
   const __half* ln_y = nullptr; const __half* ln_w16 = nullptr; const __half* ln_b16 = nullptr;
   __half* ln_x = nullptr; uint8_t* ln_x8 = nullptr; float ln_out8_scale = 1.0f;
   int precise_act = 0;
+  // output LayerNorm: C = LN(acc + bias + residual) * w + b over the whole row, inside the GEMM kernel, with an optional
+  // e4m3 copy (lno_x8) scaled by lno_out8_scale; lno_stats is the kernel's exchange buffer
+  const __half* lno_w16 = nullptr; const __half* lno_b16 = nullptr; uint8_t* lno_x8 = nullptr; float lno_out8_scale = 1.0f;
+  unsigned long long* lno_stats = nullptr;
 };
 
 int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
@@ -351,6 +359,8 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.act = l.act; g.p.out_scale = l.out_scale; g.p.status = h->status_dev;
   g.p.ln_y = l.ln_y; g.p.ln_ldy = l.k; g.p.ln_w16 = l.ln_w16; g.p.ln_b16 = l.ln_b16; g.p.ln_x = l.ln_x; g.p.ln_x8 = l.ln_x8;
   g.p.ln_out8_scale = l.ln_out8_scale; g.p.precise_act = l.precise_act;
+  g.p.lno_w16 = l.lno_w16; g.p.lno_b16 = l.lno_b16; g.p.lno_stats = l.lno_stats; g.p.lno_out8_scale = l.lno_out8_scale;
+  g.lno_x8 = l.lno_x8;
   const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
                static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
@@ -519,6 +529,11 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   // ahead of the MMAs) instead of as separate passes over the rows.
   const bool fuse_ln = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm == CRL_FUSE_LN_ON &&
                        (prec & CRL_PREC_LN_F32) == 0 && gemm_can_fuse_ln(M, std::min(3 * d, ff), d, h->num_sms);
+  // CRL_FUSE_LN_OUT: the out-projection and ff2 kernels normalise their own output rows (the CTAs holding a row block's
+  // column tiles exchange the row sums), so the sum x + sublayer(x) never crosses HBM and the two row passes per block
+  // go away. The result lands in w.x, over the residual it was computed from.
+  const bool lno = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm == CRL_FUSE_LN_OUT &&
+                   (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr && gemm_can_fuse_ln_out(M, d, h->num_sms);
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
   {
@@ -653,11 +668,15 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if (f8_attn) { o.kind = kKindF8; o.a = w.t2_8; o.w = L.wo8; o.alpha = 1.0f / (L.sa_ctx * L.sw_o); o.bias = L.bo8; }
       else if (i8) { o.kind = kKindI8; o.a = w.t2_8; o.w = L.wo_q; o.row_scale = w.t2s; o.col_scale = L.cs_o; }
       else { o.a = w.t2; o.w = L.wo; }
+      if (lno) {
+        o.c = w.x; o.lno_w16 = L.ln1w16; o.lno_b16 = L.ln1b16; o.lno_x8 = f8 ? w.x8 : nullptr; o.lno_out8_scale = L.sa_ffn;
+        o.lno_stats = w.lno_stats;
+      }
       if ((rc = linear(h, o, s)) != CRL_OK) return rc;
     }
     const __half* ffn_in;
     if (c.ln_mode == CRL_LN_POST) {
-      if (!fuse_ln &&
+      if (!fuse_ln && !lno &&
           (rc = layer_norm(h, w.y, M, d, L.ln1w, L.ln1b, w.x, f8 ? w.x8 : nullptr, L.sa_ffn, nullptr, nullptr, s, i8 ? xq : nullptr, w.xs)) != CRL_OK) return rc;
       ffn_in = w.x;
     } else {
@@ -687,9 +706,14 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       if (f8_ffn) { b.kind = kKindF8; b.a = w.t1_8; b.w = L.wff2_8; b.alpha = 1.0f / (L.sa_hid * L.sw_ff2); b.bias = L.bff2_8; }
       else if (i8) { b.kind = kKindI8; b.a = w.t1_8; b.w = L.wff2_q; b.row_scale = w.t1s; b.col_scale = L.cs_ff2; }
       else { b.a = w.t1; b.w = L.wff2; }
+      if (lno) {
+        const bool emit8 = f8 && l + 1 < c.n_layers;
+        b.c = w.x; b.lno_w16 = L.ln2w16; b.lno_b16 = L.ln2b16; b.lno_x8 = emit8 ? w.x8 : nullptr;
+        b.lno_out8_scale = emit8 ? h->layers[l + 1].sa_in : 1.0f; b.lno_stats = w.lno_stats;
+      }
       if ((rc = linear(h, b, s)) != CRL_OK) return rc;
     }
-    if (c.ln_mode == CRL_LN_POST && !(fuse_ln && l + 1 < c.n_layers)) {
+    if (c.ln_mode == CRL_LN_POST && !lno && !(fuse_ln && l + 1 < c.n_layers)) {
       const bool emit8 = f8 && l + 1 < c.n_layers;
       if ((rc = layer_norm(h, w.y, M, d, L.ln2w, L.ln2b, w.x, emit8 ? w.x8 : nullptr,
                            emit8 ? h->layers[l + 1].sa_in : 1.0f, nullptr, nullptr, s,
@@ -943,7 +967,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
       c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
   if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3 && c.dtype != CRL_DTYPE_I8) return CRL_ERR_UNSUPPORTED;
-  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_ON || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
+  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_OUT || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
   if (c.dtype == CRL_DTYPE_I8 && (c.d_model % 16 != 0 || c.d_ff % 16 != 0)) return CRL_ERR_SHAPE;
   if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&
@@ -1453,6 +1477,12 @@ int crl_linear_ex(const crl_linear_args* x) {
     g.p.ln_w16 = static_cast<const __half*>(x->ln_weight); g.p.ln_b16 = static_cast<const __half*>(x->ln_bias);
     g.p.ln_x = static_cast<__half*>(x->ln_x); g.p.ln_x8 = static_cast<uint8_t*>(x->ln_x8); g.p.ln_out8_scale = x->ln_out8_scale;
     if (x->a != (x->kind == CRL_DTYPE_F16 ? x->ln_x : x->ln_x8) || x->lda != x->k) return CRL_ERR_INVALID;
+  }
+  if (x->lno_weight != nullptr || x->lno_bias != nullptr || x->lno_scratch != nullptr || x->lno_x8 != nullptr) {
+    if (x->lno_weight == nullptr || x->lno_bias == nullptr || x->lno_scratch == nullptr || x->residual == nullptr) return CRL_ERR_INVALID;
+    g.p.lno_w16 = static_cast<const __half*>(x->lno_weight); g.p.lno_b16 = static_cast<const __half*>(x->lno_bias);
+    g.p.lno_stats = static_cast<unsigned long long*>(x->lno_scratch); g.p.lno_out8_scale = x->lno_out8_scale;
+    g.lno_x8 = x->lno_x8;
   }
   return gemm_launch(g, sms, static_cast<cudaStream_t>(x->stream));
 }

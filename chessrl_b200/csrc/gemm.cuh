@@ -51,6 +51,15 @@ struct GemmParams {
   uint8_t* ln_x8;          // [M, K] e4m3 out (nullable), pitch K
   float ln_out8_scale;
   int precise_act;         // 1: Mish into an e4m3 output in fp32 instead of on packed f16 pairs
+  // LNO kernels: the output rows are LayerNorm(acc + bias + residual) over all N columns (N <= 1024, a multiple of
+  // 256). The CTAs that hold the column tiles of a row block exchange per-row sums through `lno_stats`, one 8-byte
+  // record (sum, sum of squares) per row and column tile, preset to all-ones bits before the launch; the f16 result
+  // goes to C (which may be the residual buffer itself) and an e4m3 copy * lno_out8_scale through a second tensor map.
+  const __half* lno_w16;   // [N] f16 LayerNorm weight
+  const __half* lno_b16;   // [N] f16 LayerNorm bias
+  unsigned long long* lno_stats;   // [tiles_m][tiles_n][256]
+  int lno_x8;              // 1: the e4m3 copy is wanted
+  float lno_out8_scale;
 };
 
 #ifndef CRL_PAIR_O8_STAGES
@@ -69,9 +78,11 @@ constexpr int kLnWarps = 6;          // LNA kernels: LayerNorm warps after the e
 //   O8  = 1: the output is e4m3 (2 KB slabs), 0: f16 (4 KB slabs);
 //   RES = 1 (f16 output only): the residual slab arrives by TMA in the warp's own slab buffer, requested a
 //         tile ahead, and the result overwrites it in place before the store.
-template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0>
+//   LNO = 1 (with RES): the slab is normalised over the whole output row before it is stored (see the epilogue).
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0>
 struct GemmCfg {
   static_assert(!LNA || PAIR, "the fused LayerNorm exists for CTA pairs only");
+  static_assert(!LNO || (PAIR && RES && !O8 && !LNA), "the output LayerNorm extends the residual kernel of CTA pairs");
   static constexpr int THREADS = kGemmThreads + (LNA ? 32 * kLnWarps : 0);
   static_assert(!(RES && O8), "the residual variant writes f16");
   static_assert(!PAIR || BN == 256, "pairs work on 256 x 256 tiles");
@@ -87,10 +98,12 @@ struct GemmCfg {
   // straight from global memory (L1-resident), which needs no barrier among the epilogue warps
   static constexpr uint32_t TAB_BYTES = PAIR ? 0 : 4 * BN * 4;
   // per epilogue warp: pairs one slab (32 rows x 64 columns of the output type), single CTAs one 32 x 32 chunk
-  static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : 4096) : 2048;
+  // (LNO: the f16 slab and, behind it, the e4m3 copy's slab)
+  static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : (LNO ? 6144 : 4096)) : 2048;
   // pairs: f16 slabs leave room for five 32 KB stages (four with the int8 scale table)
   // pairs: five 32 KB stages; the f16-output kernels with a fused LayerNorm give one up for its parameter table
-  static constexpr int STAGES = PAIR ? ((LNA && !O8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
+  // (LNO kernels give one up for the second slab)
+  static constexpr int STAGES = PAIR ? (((LNA && !O8) || LNO) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
                                      : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr uint32_t LN_PRM_BYTES = LNA ? 4096 : 0;    // LayerNorm weight [1024] and bias [1024] as f16
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
@@ -308,11 +321,12 @@ __device__ __forceinline__ bool ln_wait_blocks(uint32_t words_smem, uint32_t blo
   }
 }
 
-template <int BN, int KIND, int PAIR, int RES, int O8, int LNA>
+template <int BN, int KIND, int PAIR, int RES, int O8, int LNA, int LNO = 0>
 __global__ void __launch_bounds__(kGemmThreads + (LNA ? 32 * kLnWarps : 0), 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
-  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA>;
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
+               const __grid_constant__ CUtensorMap tmX8, const GemmParams p) {
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA, LNO>;
   constexpr int BM = Cfg::BM, TM = Cfg::TM, BK = Cfg::BK, STAGES = Cfg::STAGES;
   // cluster rank (0 = leader) and the persistent worker this CTA belongs to
   const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
@@ -606,6 +620,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // two TMEM loads of 32 columns, each waited for before anything else touches its registers (a tcgen05.ld
         // fills them asynchronously); each half is then worked on as two pieces of 16 columns
         uint32_t acc[32];
+        float lsum = 0.0f, lsq = 0.0f;      // LNO: this lane's row, summed over the slab's 64 columns
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if ((i & 1) == 0) {
@@ -746,6 +761,124 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t w0 = pack_f16x2(v[h2 * 8 + 0], v[h2 * 8 + 1]), w1 = pack_f16x2(v[h2 * 8 + 2], v[h2 * 8 + 3]);
               const uint32_t w2 = pack_f16x2(v[h2 * 8 + 4], v[h2 * 8 + 5]), w3 = pack_f16x2(v[h2 * 8 + 6], v[h2 * 8 + 7]);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+              if constexpr (LNO) {
+                // statistics of the values as stored (rounded to f16), as a separate pass over the stored rows sees them
+                const uint32_t ws[4] = {w0, w1, w2, w3};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[j]));
+                  lsum += f.x + f.y;
+                  lsq = fmaf(f.x, f.x, fmaf(f.y, f.y, lsq));
+                }
+              }
+            }
+          }
+        }
+        if constexpr (LNO) {
+          // ---- LayerNorm over the whole output row. The slab holds y = acc + bias + residual as f16; this lane's row
+          // needs the sums of all N columns, which sit in 4 warps of each of the tiles_n CTAs that work on the row
+          // block's column tiles.
+          // (1) Inside the CTA: each warp leaves its partial in its own e4m3 slab buffer (unused until step 3; the
+          //     stores of the previous tile have read it); the last of the lane quarter's four warps to arrive adds
+          //     them in column order and publishes the CTA's record for these 32 rows.
+          const uint32_t slot8 = slot + 4096u;
+          asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(slot8 + 8u * lane), "f"(lsum), "f"(lsq) : "memory");
+          __syncwarp();
+          uint32_t old = 0;
+          if (lane == 0)
+            asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(ln_counter + 4u * quarter) : "memory");
+          old = __shfl_sync(0xffffffffu, old, 0);
+          const long long rec_row = (long long)rank * BM + quarter * 32 + lane;
+          if ((old & 3u) == 3u) {
+            float S = 0.0f, Q = 0.0f;
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+              // the warp with columns [64 pp, +64) of this lane quarter is epilogue warp 4 pp + ((quarter + 2) & 3)
+              const uint32_t src = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + uint32_t(4 * pp + ((quarter + 2) & 3)) * Cfg::SLOT_BYTES + 4096u + 8u * lane;
+              float a, b;
+              asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(src) : "memory");
+              S += a;
+              Q += b;
+            }
+            const unsigned long long pk = (static_cast<unsigned long long>(__float_as_uint(Q)) << 32) | __float_as_uint(S);
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.lno_stats + ((long long)mi * tiles_n + ni) * TM + rec_row), "l"(pk) : "memory");
+          }
+          // (2) Across the CTAs: poll the row's tiles_n records (each is valid as soon as it is not the preset
+          //     all-ones pattern: a record is one 8-byte store), bounded like every other wait.
+          float S = 0.0f, Q = 0.0f;
+          {
+            unsigned long long t0 = 0;
+            const unsigned long long* recs = p.lno_stats + (long long)mi * tiles_n * TM + rec_row;
+            for (int it = 0;; ++it) {
+              bool ok = true;
+              S = 0.0f; Q = 0.0f;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j < tiles_n) {
+                  unsigned long long r;
+                  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(r) : "l"(recs + (long long)j * TM) : "memory");
+                  ok = ok && r != ~0ull;
+                  S += __uint_as_float(static_cast<uint32_t>(r));
+                  Q += __uint_as_float(static_cast<uint32_t>(r >> 32));
+                }
+              }
+              if (__all_sync(0xffffffffu, ok)) break;
+              if (it == 8) t0 = global_timer_ns();
+              if (it > 8) {
+                __nanosleep(64);
+                if (global_timer_ns() - t0 > 2000000000ull) {
+                  alive = false;
+                  break;
+                }
+              }
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+              if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
+              break;
+            }
+          }
+          // (3) Normalise the slab in place (fp32 statistics, f16 affine: the arithmetic of the row kernels) and
+          //     derive the e4m3 copy.
+          const float inv_n = 1.0f / static_cast<float>(p.N);
+          const float mean = S * inv_n;
+          const float rstd = rsqrtf(fmaxf(Q * inv_n - mean * mean, 0.0f) + 1e-5f);
+          const float shift = -mean * rstd;
+          const __half2 s8 = __floats2half2_rn(p.lno_out8_scale, p.lno_out8_scale);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w8[4];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int q = i * 2 + h2;
+              const uint32_t off = slot + lane * 128 + ((q ^ (lane & 7)) << 4);
+              uint4 u;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off) : "memory");
+              const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.lno_w16 + c0 + q * 8));
+              const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.lno_b16 + c0 + q * 8));
+              const __half2* h = reinterpret_cast<const __half2*>(&u);
+              const __half2* wh = reinterpret_cast<const __half2*>(&w4);
+              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+              __half2 y2[4];
+              uint32_t o16[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
+                y2[j] = __hfma2(xn, wh[j], bh[j]);
+                o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]) : "memory");
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+                w8[h2 * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                                 (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+              }
+            }
+            if (p.lno_x8 != 0) {
+              const uint32_t off8 = slot8 + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]) : "memory");
             }
           }
         }
@@ -754,6 +887,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
           // rows and columns beyond the matrix are clipped by the TMA unit
           tma_store_2d(&tmC, slot, c0, m0 + quarter * 32);
+          if constexpr (LNO) {
+            if (p.lno_x8 != 0) tma_store_2d(&tmX8, slot + 4096u, c0, m0 + quarter * 32);
+          }
           bulk_commit();
         }
         if (RES != 0 && tma_res) {

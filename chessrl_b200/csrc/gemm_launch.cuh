@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -57,6 +58,7 @@ inline int make_tmap_2d(CUtensorMap* out, const void* ptr, int esz, uint64_t inn
 }
 
 struct GemmArgs {
+  void* lno_x8 = nullptr;       // LNO kernels: [M, N] e4m3 copy of the normalised rows (nullable)
   int kind = kKindF16;          // MmaKind: element type of A and W
   const void* A = nullptr;      // [M, lda]
   long long lda = 0;            // elements
@@ -80,14 +82,21 @@ inline bool gemm_can_fuse_ln(long long M, int N, int K, int num_sms) {
   return N >= 256 && K <= 1024 && K % 8 == 0 && (M + 255) / 256 >= 2ll * (num_sms / 2);
 }
 
-template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0>
+// The GEMM that also normalises its output rows (LNO kernels): the CTAs holding the column tiles of a row block
+// exchange row sums, so every CTA pair has to be resident at once and busy: N a multiple of 256 up to 1024, at least
+// one tile per pair.
+inline bool gemm_can_fuse_ln_out(long long M, int N, int num_sms) {
+  return N % 256 == 0 && N <= 1024 && ((M + 255) / 256) * (N / 256) >= num_sms / 2;
+}
+
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA>;
+  using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA, LNO>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -118,10 +127,21 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       make_tmap_2d(&tmR, prm.residual, 2, prm.N, prm.M, static_cast<uint64_t>(prm.ldr) * 2, 32, 128) == kOk)
     prm.use_tma_res = 1;
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
+  // LNO: the e4m3 copy of the normalised rows leaves through a tensor map of its own (pitch N)
+  CUtensorMap tmX8;
+  std::memset(&tmX8, 0, sizeof(tmX8));
+  if constexpr (LNO != 0) {
+    if (!prm.use_tma_res || prm.lno_stats == nullptr || prm.lno_w16 == nullptr || prm.lno_b16 == nullptr) return kErrInvalid;
+    prm.lno_x8 = 0;
+    if (a.lno_x8 != nullptr) {
+      if (make_tmap_2d(&tmX8, a.lno_x8, 1, prm.N, prm.M, static_cast<uint64_t>(prm.N), 32, 64) != kOk) return kErrShape;
+      prm.lno_x8 = 1;
+    }
+  }
   if constexpr (PAIR) {
     // one 2-CTA cluster per pair of SMs (LNA: a pair owns whole row blocks, so no more pairs than row blocks)
     const int units = LNA ? (a.p.M + Cfg::TM - 1) / Cfg::TM : tiles;
-    const int pairs = units < num_sms / 2 ? units : num_sms / 2;
+    int pairs = units < num_sms / 2 ? units : num_sms / 2;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
     cfg.blockDim = dim3(Cfg::THREADS);
@@ -132,10 +152,28 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA>, tmA, tmB, tmC, tmR, prm) == cudaSuccess ? kOk : kErrCuda;
+    if constexpr (LNO != 0) {
+      // CTAs of this kernel wait for one another: launch no more pairs than the device holds at once
+      static int resident[64] = {};
+      if (dev < 0 || dev >= 64) return kErrInvalid;
+      if (resident[dev] == 0) {
+        int n = 0;
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * (num_sms / 2)));
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, &cfg) != cudaSuccess || n <= 0)
+          return kErrCuda;
+        resident[dev] = n;
+        if (std::getenv("CRL_DEBUG") != nullptr) std::fprintf(stderr, "chessrl_b200: %d CTA pairs resident at once on device %d\n", n, dev);
+      }
+      if (pairs > resident[dev]) pairs = resident[dev];
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+      // every record of the exchange buffer starts as the "not written yet" pattern
+      const size_t recs = static_cast<size_t>((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN) * Cfg::TM;
+      if (cudaMemsetAsync(prm.lno_stats, 0xFF, recs * sizeof(unsigned long long), stream) != cudaSuccess) return kErrCuda;
+    }
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, tmA, tmB, tmC, tmR, tmX8, prm) == cudaSuccess ? kOk : kErrCuda;
   } else {
     const int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_tn_kernel<BN, KIND, 0, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, prm);
+    gemm_tn_kernel<BN, KIND, 0, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, tmX8, prm);
     return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
   }
 }
@@ -157,6 +195,17 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       return a.p.out_dtype == kOutE4M3 ? gemm_launch_t<256, KIND, 1, 0, 1, 1>(a, num_sms, stream)
                                        : gemm_launch_t<256, KIND, 1, 0, 0, 1>(a, num_sms, stream);
     }
+  }
+  if (a.p.lno_stats != nullptr) {
+    // output rows normalised inside the kernel: the residual kernel of CTA pairs, f16 / e4m3 operands
+    const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
+                         (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
+    if (KIND == kKindI8 || !gemm_can_fuse_ln_out(a.p.M, a.p.N, num_sms) || a.p.out_dtype != kOutF16 || !out_map_ok(a.p) ||
+        !res_tma || a.p.col_scale != nullptr || a.p.row_scale != nullptr || a.p.ln_y != nullptr || a.p.lno_w16 == nullptr ||
+        a.p.lno_b16 == nullptr || (reinterpret_cast<uintptr_t>(a.p.lno_w16) & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
+      return kErrUnsupported;
+    if constexpr (KIND != kKindI8) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);
   }
   // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&

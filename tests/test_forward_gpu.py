@@ -686,6 +686,42 @@ def test_gemm_fused_layernorm_equals_separate_passes(dtype):
         assert (outs[0][0][:64] - bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal))[legal].abs().max() <= POLICY_TOL
 
 
+@pytest.mark.parametrize("dtype,d", [(0, 512), (1, 512), (1, 256)])
+def test_layernorm_inside_the_producing_gemm_matches_separate_passes(dtype, d):
+    """crl_config.fuse_layernorm = CRL_FUSE_LN_OUT: the out-projection and ff2 kernels of large post-LN passes
+    normalise their own output rows (d = 512: two column tiles per row block, so two CTA pairs exchange row sums).
+    The row statistics are summed in another order than the stand-alone kernel's, so the results agree within f16
+    rounding rather than bit for bit; two fused runs are identical, and both LayerNorm launches of every block go."""
+    from chessrl_b200 import Engine, EngineConfig, positions
+    import chessrl_b200 as crl
+    cfg = bt4spec.SpecConfig.baseline(3, d, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=17)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    b = 4 * sms + 37
+    pos = positions.playout_positions(b, seed=23)
+    planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
+    outs = []
+    for fuse in (crl.FUSE_LN_OUT, crl.FUSE_LN_OUT, crl.FUSE_LN_OFF):
+        eng = Engine(EngineConfig(dtype=dtype, fuse_layernorm=fuse, **cfg.to_dict()))
+        eng.load_state_dict(sd)
+        if dtype == crl.DTYPE_F8E4M3:
+            eng.calibrate(planes[:256])
+        out = eng.forward(planes, legal_mask=bits)
+        torch.cuda.synchronize()
+        rc, st = eng.last_status()
+        assert rc == 0 and st == 0
+        outs.append((out["policy"].cpu(), out["wdl"].cpu(), eng.last_launch_count()))
+        eng.close()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert outs[0][2] == outs[2][2] - 2 * 3
+    tol = 2e-3 if dtype == 0 else 2e-2           # FP8: a flipped f16 rounding can move an e4m3 rounding downstream
+    assert (outs[0][0] - outs[2][0]).abs().max() <= tol and (outs[0][1] - outs[2][1]).abs().max() <= tol
+    if dtype == 0:
+        ref = oracle_out(cfg, sd, pos["planes112"].float().view(b, 64, 112)[:64])
+        legal = torch.from_numpy(np.unpackbits(pos["legal1858"].numpy()[:64], axis=1, bitorder="little")[:, :1858].astype(bool))
+        assert (outs[0][0][:64] - bt4spec.apply_policy_mask(ref["policy"], legal_bits=legal))[legal].abs().max() <= POLICY_TOL
+
+
 def test_determinism_and_output_guards():
     """Two runs give identical bits, and nothing is written outside the rows and columns the call owns:
     outputs are carved out of larger buffers whose padding keeps its canary value."""

@@ -303,3 +303,84 @@ def test_layernorm_fusion_is_refused_where_it_cannot_run(lib):
     assert lib.crl_linear_ex(ctypes.byref(a)) == -8
     torch.cuda.synchronize()
     assert bool((c == 3.0).all())
+
+
+@pytest.mark.parametrize("kind,n,k,in_place,want8", [(1, 1024, 1024, True, True), (1, 1024, 1536, True, True),
+                                                     (0, 1024, 1024, False, False), (1, 512, 1024, False, True),
+                                                     (0, 256, 512, True, True)])
+def test_layernorm_of_the_output_rows_inside_the_gemm(lib, kind, n, k, in_place, want8):
+    """LNO kernels: c = LayerNorm(a @ w.T * alpha + bias + residual) over the n columns, the row sums exchanged between
+    the CTAs that hold the row block's column tiles. Checked against torch on the GPU: the pre-norm sum in fp32 from
+    the same operands, rounded to f16 (what the kernel normalises), then layer_norm. M is ragged (the last row block
+    is partial) and gives every CTA pair several tiles; `in_place` writes the result over the residual."""
+    import ctypes
+    from chessrl_b200 import _lib as L
+    torch.manual_seed(n + k + kind)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    m = 256 * ((3 * sms) // (n // 256)) + 256 * 5 + 77
+    a = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda")
+    if kind == 1:
+        a, w, alpha = a.to(torch.float8_e4m3fn), w.to(torch.float8_e4m3fn), 1.0 / 32.0
+    else:
+        a, w, alpha = a.half(), (w * 0.05).half(), 1.0
+    bias = torch.randn(n, device="cuda")
+    res = (torch.randn(m, n, device="cuda") * 1.5 + 0.3).half()
+    gamma = (1.0 + 0.1 * torch.randn(n, device="cuda")).half()
+    beta = (0.1 * torch.randn(n, device="cuda")).half()
+    s8 = 448.0 / 6.0
+    pre = (alpha * (a.float() @ w.float().t()) + bias + res.float()).half().float()
+    want = torch.nn.functional.layer_norm(pre, (n,), gamma.float(), beta.float(), 1e-5)
+    c = res.clone() if in_place else torch.full((m + 2, n), 7.0, device="cuda", dtype=torch.float16)
+    x8 = torch.full((m + 2, n), 0x55, device="cuda", dtype=torch.uint8)
+    scratch = torch.zeros(256 * ((m + 255) // 256) * (n // 256), device="cuda", dtype=torch.int64)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    x = L.LinearArgs()
+    x.kind, x.out_dtype = kind, 0
+    x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
+    x.m, x.n, x.k = m, n, k
+    x.bias, x.residual, x.ldr = bias.data_ptr(), (c if in_place else res).data_ptr(), n
+    x.alpha, x.out_scale = alpha, 1.0
+    x.device_status = status.data_ptr()
+    x.lno_weight, x.lno_bias, x.lno_scratch = gamma.data_ptr(), beta.data_ptr(), scratch.data_ptr()
+    x.lno_x8, x.lno_out8_scale = (x8.data_ptr() if want8 else None), s8
+    for _ in range(2):      # the second call finds the exchange buffer used
+        if in_place:
+            c.copy_(res)
+        rc = lib.crl_linear_ex(ctypes.byref(x))
+        torch.cuda.synchronize()
+        assert rc == 0 and int(status[0]) == 0, (rc, int(status[0]))
+    got = c[:m].float()
+    # one f16 rounding of the pre-norm sum may fall the other way (fp32 summation order): a step of it times rstd ~ 1
+    assert_close_elementwise(got, want, 6e-3 + 2e-3 * want.abs())
+    assert (got - want).abs().mean().item() < 6e-4
+    if not in_place:
+        assert bool((c[m:] == 7.0).all()), "rows beyond M were written"
+    if want8:
+        ref8 = (got * s8).clamp(-448, 448)
+        assert_close_elementwise(e4m3_decode(x8[:m]), ref8, 0.5 * e4m3_step(ref8) + 2e-3 * ref8.abs() + 1e-6)
+        assert bool((x8[m:] == 0x55).all()), "e4m3 rows beyond M were written"
+    else:
+        assert bool((x8 == 0x55).all())
+
+
+def test_output_layernorm_is_refused_where_it_cannot_run(lib):
+    """Too few tiles for the CTA pairs, a width that is no multiple of 256, int8 operands: CRL_ERR_UNSUPPORTED."""
+    import ctypes
+    from chessrl_b200 import _lib as L
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for kind, m, n in ((0, 2048, 1024), (0, 65536, 768 + 64), (2, 65536, 1024)):
+        k = 256
+        a = torch.zeros(m, k, device="cuda", dtype=torch.int8 if kind == 2 else torch.float16)
+        w = torch.zeros(n, k, device="cuda", dtype=a.dtype)
+        g = torch.ones(n, device="cuda", dtype=torch.float16)
+        c = torch.full((m, n), 3.0, device="cuda", dtype=torch.float16)
+        scratch = torch.zeros(256 * ((m + 255) // 256) * ((n + 255) // 256), device="cuda", dtype=torch.int64)
+        x = L.LinearArgs()
+        x.kind, x.out_dtype, x.a, x.lda, x.w, x.ldw, x.c, x.ldc = kind, 0, a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
+        x.m, x.n, x.k, x.alpha, x.device_status = m, n, k, 1.0, status.data_ptr()
+        x.residual, x.ldr = c.data_ptr(), n
+        x.lno_weight, x.lno_bias, x.lno_scratch = g.data_ptr(), g.data_ptr(), scratch.data_ptr()
+        assert lib.crl_linear_ex(ctypes.byref(x)) == -8, (kind, m, n)
+        torch.cuda.synchronize()
+        assert bool((c == 3.0).all())
