@@ -18,8 +18,8 @@ Small repeatable programs for a profiler capture (`-k regex:<kernel>`); they pri
         LayerNorm of the output rows inside the kernel, in place, with an e4m3 copy, through `crl_linear_ex`)
     python bench.py --case forward <f16|f8|i8> <positions> [chunk [fuse_layernorm [precision]]]
         the BT4-shaped forward pass: plain timing of three passes, then one pass with the library's per-launch
-        CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm 1 = LayerNorms inside the
-        ff1 / QKV GEMM kernels, 2 = inside the out-projection / ff2 kernels; precision = CRL_PREC_* bit mask)
+        CUDA events, grouped by kernel and shape (chunk 0 = default; fuse_layernorm: 0 = the library's choice,
+        1 = LayerNorms inside the ff1 / QKV GEMM kernels, 2 = inside the out-projection / ff2 kernels, 3 = separate passes; precision = CRL_PREC_* bit mask)
 """
 import argparse
 import json
@@ -277,7 +277,7 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
     from chessrl_b200 import _lib
     lib = _lib.load()
     dev = "cuda"
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
     g = torch.Generator(device=dev).manual_seed(0)
     if kind == 1:
         a = torch.randn(M, K, device=dev, generator=g).to(torch.float8_e4m3fn)
@@ -303,7 +303,7 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
         gamma = torch.ones(N, device=dev, dtype=torch.float16)
         beta = torch.zeros(N, device=dev, dtype=torch.float16)
         x8 = torch.empty(M, N, device=dev, dtype=torch.uint8)
-        scratch = torch.zeros(256 * ((M + 255) // 256) * ((N + 255) // 256), device=dev, dtype=torch.int64)
+        scratch = torch.zeros(2048 * ((M + 255) // 256), device=dev, dtype=torch.int64)
         x = _lib.LinearArgs()
         x.kind, x.out_dtype = kind, 0
         x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), K, w.data_ptr(), K, r.data_ptr(), N
@@ -329,6 +329,8 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
     us = e0.elapsed_time(e1) / launches * 1e3
     print(f"gemm kind={kind} M={M} N={N} K={K} out={out} act={act} res={residual}: rc {rc} status {status[0].item()}  "
           f"{us:.1f} us/launch  {2.0 * M * N * K / us / 1e6:.1f} TFLOP/s", flush=True)
+    if os.environ.get("CRL_PROBE"):
+        print("probe", [int(v) * 16 for v in status[8:24].tolist()], flush=True)
     return 0 if rc == 0 and status[0].item() == 0 else 1
 
 

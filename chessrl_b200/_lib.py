@@ -23,7 +23,7 @@ PACKED104_BYTES = 840
 MASK_NONE, MASK_BITS, MASK_ADDITIVE, MASK_FROM_RECORDS = 0, 1, 2, 3
 OUT_F32, OUT_F16 = 0, 1
 VOCAB_NATIVE, VOCAB_RL1929 = 0, 1
-FUSE_LN_OFF, FUSE_LN_ON, FUSE_LN_OUT = 0, 1, 2
+FUSE_LN_AUTO, FUSE_LN_ON, FUSE_LN_OUT, FUSE_LN_OFF = 0, 1, 2, 3
 PREC_QKV_F16, PREC_LN_F32, PREC_MISH_F32, PREC_ATTN_F32, PREC_FFN_F16, PREC_ATTN_GEMM_F16 = 1, 2, 4, 8, 16, 32
 
 EXPORTS = [

@@ -301,9 +301,9 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc, int64_t total) {
   w.v2 = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(total) * 236 : 0));
-  // one 8-byte record per row and 256-column tile, rows rounded up to whole 256-row blocks
-  const bool lno = c.fuse_layernorm == CRL_FUSE_LN_OUT && c.ln_mode == CRL_LN_POST && c.dtype != CRL_DTYPE_I8 && d % 256 == 0;
-  w.lno_stats = reinterpret_cast<unsigned long long*>(take(lno ? align_up(M, 256) * (d / 256) * 8 : 0));
+  const bool lno = (c.fuse_layernorm == CRL_FUSE_LN_OUT || c.fuse_layernorm == CRL_FUSE_LN_AUTO) && c.ln_mode == CRL_LN_POST &&
+                   c.dtype != CRL_DTYPE_I8 && d % 256 == 0;
+  w.lno_stats = reinterpret_cast<unsigned long long*>(take(lno ? gemm_ln_out_scratch_bytes(static_cast<long long>(M)) : 0));
   w.total = off;
   return w;
 }
@@ -360,7 +360,7 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.ln_y = l.ln_y; g.p.ln_ldy = l.k; g.p.ln_w16 = l.ln_w16; g.p.ln_b16 = l.ln_b16; g.p.ln_x = l.ln_x; g.p.ln_x8 = l.ln_x8;
   g.p.ln_out8_scale = l.ln_out8_scale; g.p.precise_act = l.precise_act;
   g.p.lno_w16 = l.lno_w16; g.p.lno_b16 = l.lno_b16; g.p.lno_stats = l.lno_stats; g.p.lno_out8_scale = l.lno_out8_scale;
-  g.lno_x8 = l.lno_x8;
+  g.p.lno_x8 = l.lno_x8;
   const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
                static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
@@ -529,11 +529,14 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   // ahead of the MMAs) instead of as separate passes over the rows.
   const bool fuse_ln = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm == CRL_FUSE_LN_ON &&
                        (prec & CRL_PREC_LN_F32) == 0 && gemm_can_fuse_ln(M, std::min(3 * d, ff), d, h->num_sms);
-  // CRL_FUSE_LN_OUT: the out-projection and ff2 kernels normalise their own output rows (the CTAs holding a row block's
-  // column tiles exchange the row sums), so the sum x + sublayer(x) never crosses HBM and the two row passes per block
-  // go away. The result lands in w.x, over the residual it was computed from.
-  const bool lno = !calib && !i8 && c.ln_mode == CRL_LN_POST && c.fuse_layernorm == CRL_FUSE_LN_OUT &&
-                   (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr && gemm_can_fuse_ln_out(M, d, h->num_sms);
+  // CRL_FUSE_LN_OUT: the out-projection and ff2 kernels normalise their own output rows (the warps holding a row's
+  // slabs, in the CTAs working on the row block's column tiles, exchange the row sums), so the sum x + sublayer(x)
+  // never crosses HBM and the two row passes per block go away. The result lands in w.x, over the residual it was
+  // computed from.
+  // (CRL_FUSE_LN_AUTO takes it from four tiles per CTA pair on: below that it measures neither faster nor slower.)
+  const bool lno = !calib && !i8 && c.ln_mode == CRL_LN_POST && (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr &&
+                   ((c.fuse_layernorm == CRL_FUSE_LN_OUT && gemm_can_fuse_ln_out(M, d, h->num_sms)) ||
+                    (c.fuse_layernorm == CRL_FUSE_LN_AUTO && gemm_can_fuse_ln_out(M / 4, d, h->num_sms)));
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
   {
@@ -967,7 +970,7 @@ int crl_create(const crl_config* cfg, int device, crl_handle** out) {
       c.bias_mode < 0 || c.bias_mode > 3 || c.policy_mode < 0 || c.policy_mode > 3 || c.value_mode < 0 || c.value_mode > 2)
     return CRL_ERR_INVALID;
   if (c.dtype != CRL_DTYPE_F16 && c.dtype != CRL_DTYPE_F8E4M3 && c.dtype != CRL_DTYPE_I8) return CRL_ERR_UNSUPPORTED;
-  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_OUT || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
+  if (c.fuse_layernorm < 0 || c.fuse_layernorm > CRL_FUSE_LN_OFF || c.precision < 0 || c.precision > 63) return CRL_ERR_INVALID;
   if (c.dtype == CRL_DTYPE_I8 && (c.d_model % 16 != 0 || c.d_ff % 16 != 0)) return CRL_ERR_SHAPE;
   if (c.policy_mode == CRL_POLICY_LM_HEAD && (c.lm_vocab <= 0 || c.lm_vocab > 2048)) return CRL_ERR_SHAPE;
   if (c.bias_mode == CRL_BIAS_SMOLGEN &&
@@ -1482,7 +1485,7 @@ int crl_linear_ex(const crl_linear_args* x) {
     if (x->lno_weight == nullptr || x->lno_bias == nullptr || x->lno_scratch == nullptr || x->residual == nullptr) return CRL_ERR_INVALID;
     g.p.lno_w16 = static_cast<const __half*>(x->lno_weight); g.p.lno_b16 = static_cast<const __half*>(x->lno_bias);
     g.p.lno_stats = static_cast<unsigned long long*>(x->lno_scratch); g.p.lno_out8_scale = x->lno_out8_scale;
-    g.lno_x8 = x->lno_x8;
+    g.p.lno_x8 = static_cast<uint8_t*>(x->lno_x8);
   }
   return gemm_launch(g, sms, static_cast<cudaStream_t>(x->stream));
 }

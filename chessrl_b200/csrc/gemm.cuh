@@ -52,13 +52,14 @@ struct GemmParams {
   float ln_out8_scale;
   int precise_act;         // 1: Mish into an e4m3 output in fp32 instead of on packed f16 pairs
   // LNO kernels: the output rows are LayerNorm(acc + bias + residual) over all N columns (N <= 1024, a multiple of
-  // 256). The CTAs that hold the column tiles of a row block exchange per-row sums through `lno_stats`, one 8-byte
-  // record (sum, sum of squares) per row and column tile, preset to all-ones bits before the launch; the f16 result
-  // goes to C (which may be the residual buffer itself) and an e4m3 copy * lno_out8_scale through a second tensor map.
+  // 256). The warps that hold the 128-column slabs of a row - in the CTAs working on the row block's column tiles -
+  // exchange per-row sums through `lno_stats`, one 8-byte record (sum, sum of squares) per row and slab, preset to
+  // all-ones bits before the launch. The f16 result goes to C (which may be the residual buffer itself), an e4m3
+  // copy * lno_out8_scale to lno_x8.
   const __half* lno_w16;   // [N] f16 LayerNorm weight
   const __half* lno_b16;   // [N] f16 LayerNorm bias
-  unsigned long long* lno_stats;   // [tiles_m][tiles_n][256]
-  int lno_x8;              // 1: the e4m3 copy is wanted
+  unsigned long long* lno_stats;   // [tiles_m][8 slabs][256 rows]
+  uint8_t* lno_x8;         // [M, N] e4m3 copy (nullable)
   float lno_out8_scale;
 };
 
@@ -98,12 +99,12 @@ struct GemmCfg {
   // straight from global memory (L1-resident), which needs no barrier among the epilogue warps
   static constexpr uint32_t TAB_BYTES = PAIR ? 0 : 4 * BN * 4;
   // per epilogue warp: pairs one slab (32 rows x 64 columns of the output type), single CTAs one 32 x 32 chunk
-  // (LNO: the f16 slab and, behind it, the e4m3 copy's slab)
-  static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : (LNO ? 6144 : 4096)) : 2048;
+  // (LNO: a 32 x 128 slab as two sub-slabs of 64 columns)
+  static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : (LNO ? 8192 : 4096)) : 2048;
   // pairs: f16 slabs leave room for five 32 KB stages (four with the int8 scale table)
   // pairs: five 32 KB stages; the f16-output kernels with a fused LayerNorm give one up for its parameter table
-  // (LNO kernels give one up for the second slab)
-  static constexpr int STAGES = PAIR ? (((LNA && !O8) || LNO) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5))
+  // (LNO kernels keep three: their second slab per warp takes the room of two)
+  static constexpr int STAGES = PAIR ? (LNO ? 3 : ((LNA && !O8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5)))
                                      : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr uint32_t LN_PRM_BYTES = LNA ? 4096 : 0;    // LayerNorm weight [1024] and bias [1024] as f16
   static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 columns
@@ -113,11 +114,11 @@ struct GemmCfg {
   static constexpr uint32_t LN_PRM_OFF = EPI_OFF + TAB_BYTES + kEpiWarps * SLOT_BYTES;
   static constexpr uint32_t BAR_OFF = LN_PRM_OFF + LN_PRM_BYTES;
   // barrier region: [0,128) ring (2 x STAGES <= 12) and accumulator (4) mbarriers, [128,144) the TMEM address slot,
-  // [144, 144 + 8 x 16) one mbarrier per epilogue warp (residual slab), then the LayerNorm progress words
+  // [144, 144 + 16 x 16) the epilogue warps' mbarriers (residual slabs), then the LayerNorm progress words
   static_assert(2 * STAGES + 4 <= 16, "the ring and accumulator barriers share 128 bytes");
   static constexpr uint32_t TMEM_SLOT_OFF = BAR_OFF + 128;
   static constexpr uint32_t RBAR_OFF = BAR_OFF + 144;
-  static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 8;
+  static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 16;     // (two per warp: LNO kernels have two slabs)
   static constexpr uint32_t USED_BYTES = LN_COUNTER_OFF + 48;   // [0] epilogue warps' arrivals, [4 + w] blocks done by LayerNorm warp w
   static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + ((PAIR && (!O8 || STAGES > 5)) ? 496 : 896) /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
@@ -380,11 +381,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int w = 0; w < kEpiWarps; ++w) mbar_init(base + Cfg::RBAR_OFF + 8u * w, 1);
+    for (int w = 0; w < 2 * kEpiWarps; ++w) mbar_init(base + Cfg::RBAR_OFF + 8u * w, 1);
     for (int w = 0; w < 12; ++w) asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(ln_counter + 4u * w), "r"(0u) : "memory");
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), kEpiWarps * (PAIR ? 2 : 1));   // one arrival per epilogue warp (of both CTAs)
+      // one arrival per epilogue warp (of both CTAs) that drains the buffer: all 16, or the 8 of a set (LNO)
+      mbar_init(tempty_bar(a), (LNO ? kEpiWarps / 2 : kEpiWarps) * (PAIR ? 2 : 1));
     }
     mbar_fence_init();
   }
@@ -518,7 +520,250 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int et = threadIdx.x - 64;        // 0..511 among the epilogue threads
     float* bias_s = reinterpret_cast<float*>(smem + Cfg::EPI_OFF);                  // [2][BN]
     float* cs_s = bias_s + 2 * BN;                                                  // [2][BN] per-column scales (int8)
-    if constexpr (PAIR) {
+    if constexpr (LNO) {
+      // Slab epilogue with the LayerNorm of the output row. The 16 epilogue warps form two sets of 8 that take the
+      // worker's tiles in turn (set s drains accumulator buffer s), so that a warp has two tile times for its chain of
+      // dependent waits: accumulator -> y = acc + bias + residual as f16 into the warp's 32 x 128 slab (over the
+      // residual TMA put there) -> the row's sum and sum of squares over these 128 columns into the statistics
+      // record of (row, slab) -> the 2 tiles_n records of the row, written by the warps that hold the row's other
+      // slabs in this CTA and in the CTAs working on the row block's other column tiles -> normalise in place ->
+      // TMA store (f16) and plain stores (e4m3 copy) -> residual slab of the set's next tile.
+      // (The shared-memory loads and stores below are volatile asm without a memory clobber: they keep their order among
+      // themselves and with every barrier, fence and TMA operation - all volatile asm too - while the read-only
+      // parameter loads around them stay free to be scheduled early.)
+      const int set = ew >> 3;
+      const int half = (ew >> 2) & 1;          // columns [128 half, +128) of the CTA's 256
+      const uint32_t slab = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + ew * Cfg::SLOT_BYTES;     // two 32 x 64 sub-slabs
+      const uint32_t rbar = base + Cfg::RBAR_OFF + 8u * ew;
+      const int slabs = 2 * tiles_n;
+      bool res_pending = false;
+      uint32_t pending_ph = 0;
+      auto res_issue = [&](int i) {
+        int rm, rn;
+        tile_of(i, rm, rn);
+        pending_ph = (i >> 1) & 1u;
+        if (lane == 0) {
+          mbar_expect_tx(rbar, 8192u);
+          tma_load_2d(slab, &tmR, rn * BN + half * 128, rm * TM + rank * BM + quarter * 32, rbar);
+          tma_load_2d(slab + 4096u, &tmR, rn * BN + half * 128 + 64, rm * TM + rank * BM + quarter * 32, rbar);
+        }
+        res_pending = true;
+      };
+      auto exists = [&](int i) {
+        int rm, rn;
+        return tile_of(i, rm, rn);
+      };
+      if (exists(set)) res_issue(set);
+      const __half2 s8 = __floats2half2_rn(p.lno_out8_scale, p.lno_out8_scale);
+      const float inv_n = 1.0f / static_cast<float>(p.N);
+      const float a_scale = p.alpha;
+      // with an e4m3 copy wanted (FP8 engine) the normalisation runs on packed f16 pairs: rstd and the shift rounded
+      // to f16 cost the f16 rows one more rounding, far below the e4m3 steps of everything that reads them
+      const bool packed = p.lno_x8 != nullptr && p.precise_act == 0;
+      bool alive = true;
+      int mi = 0, ni = 0;
+      for (int local = set; tile_of(local, mi, ni); local += 2) {
+        const uint32_t ph = (local >> 1) & 1u;      // the set's k-th tile: accumulator buffer and slab phase k & 1
+        if (!mbar_wait(tfull_bar(set), ph)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        if (!mbar_wait(rbar, ph)) {      // the residual slab has landed
+          alive = false;
+          break;
+        }
+        res_pending = false;
+        {
+          // the residual slab of the set's next tile can only land once this tile's stores have read the buffer:
+          // have it waiting in L2 by then
+          int rm, rn;
+          if (lane == 0 && tile_of(local + 2, rm, rn)) {
+            tma_prefetch_l2_2d(&tmR, rn * BN + half * 128, rm * TM + rank * BM + quarter * 32);
+            tma_prefetch_l2_2d(&tmR, rn * BN + half * 128 + 64, rm * TM + rank * BM + quarter * 32);
+          }
+        }
+        const int c0 = ni * BN + half * 128;
+        const int row0 = mi * TM + rank * BM + quarter * 32;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(set * BN + half * 128);
+        uint32_t acc[32];
+        float lsum = 0.0f, lsq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if ((i & 1) == 0) {
+            tmem_ld_32x32(taddr + 16u * i, acc);
+            tmem_ld_wait();
+            if (i == 6) {
+              // the last columns sit in registers: the accumulator buffer goes back to the MMA warp
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(set), 0));   // the leader's barrier
+                else mbar_arrive(tempty_bar(set));
+              }
+            }
+          }
+          float v[16];
+          if (p.bias != nullptr) {
+            const float4* b4p = reinterpret_cast<const float4*>(p.bias + c0 + i * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 b4 = __ldg(b4p + q);
+              v[q * 4] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4]), a_scale, b4.x);
+              v[q * 4 + 1] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 1]), a_scale, b4.y);
+              v[q * 4 + 2] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 2]), a_scale, b4.z);
+              v[q * 4 + 3] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 3]), a_scale, b4.w);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(acc[(i & 1) * 16 + j]) * a_scale;
+          }
+          if (p.act == kActMish) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = act_mish(v[j]);
+          } else if (p.act == kActGelu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = act_gelu(v[j]);
+          } else if (p.act == kActRelu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.0f);
+          }
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int q = (i & 3) * 2 + h2;      // 16-byte chunk of the sub-slab's 128-byte row
+            const uint32_t off = slab + 4096u * (i >> 2) + lane * 128 + ((q ^ (lane & 7)) << 4);
+            uint4 u;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off));
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+            uint32_t ws[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(h[j]);
+              const float y0 = v[h2 * 8 + 2 * j] + f.x, y1 = v[h2 * 8 + 2 * j + 1] + f.y;
+              ws[j] = pack_f16x2(y0, y1);
+              // row statistics from the fp32 sums (the stored f16 values differ from them by their rounding only)
+              lsum += y0 + y1;
+              lsq = fmaf(y0, y0, fmaf(y1, y1, lsq));
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]));
+          }
+        }
+        const unsigned long long* recs = p.lno_stats + (long long)mi * 8 * TM + rank * BM + quarter * 32 + lane;
+        {
+          const unsigned long long pk = (static_cast<unsigned long long>(__float_as_uint(lsq)) << 32) | __float_as_uint(lsum);
+          asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(recs + (long long)(ni * 2 + half) * TM), "l"(pk) : "memory");
+        }
+        // the row's records (each is valid as soon as it is not the preset all-ones pattern: a record is one 8-byte
+        // store), added in a fixed order: a row's result does not depend on who computes it
+        float S = 0.0f, Q = 0.0f;
+        {
+          unsigned long long t0 = 0;
+          for (int it = 0;; ++it) {
+            bool ok = true;
+            unsigned long long r[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              r[j] = 0ull;
+              if (j < slabs) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(r[j]) : "l"(recs + (long long)j * TM) : "memory");
+            }
+            S = 0.0f; Q = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              ok = ok && r[j] != ~0ull;
+              S += __uint_as_float(static_cast<uint32_t>(r[j]));
+              Q += __uint_as_float(static_cast<uint32_t>(r[j] >> 32));
+            }
+            if (__all_sync(0xffffffffu, ok)) break;
+            if (it == 8) t0 = global_timer_ns();
+            if (it > 8) {
+              __nanosleep(64);
+              const bool late = global_timer_ns() - t0 > 2000000000ull;
+              if (__any_sync(0xffffffffu, late)) {
+                alive = false;
+                break;
+              }
+            }
+          }
+          if (!alive) break;
+        }
+        const float mean = S * inv_n;
+        const float rstd = rsqrtf(fmaxf(Q * inv_n - mean * mean, 0.0f) + 1e-5f);
+        const float shift = -mean * rstd;
+        const bool row_ok = row0 + lane < p.M;
+        const __half2 rstd2 = __floats2half2_rn(rstd, rstd), shift2 = __floats2half2_rn(shift, shift);
+        uint32_t w8[32];      // the e4m3 copy of this lane's 128 columns
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int q = (i4 & 3) * 2 + h2;
+            const uint32_t off = slab + 4096u * (i4 >> 2) + lane * 128 + ((q ^ (lane & 7)) << 4);
+            uint4 u;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off));
+            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.lno_w16 + c0 + i4 * 16 + h2 * 8));
+            const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.lno_b16 + c0 + i4 * 16 + h2 * 8));
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+            const __half2* wh = reinterpret_cast<const __half2*>(&w4);
+            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+            __half2 y2[4];
+            uint32_t o16[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __half2 xn;
+              if (packed) {
+                xn = __hfma2(h[j], rstd2, shift2);
+              } else {
+                const float2 f = __half22float2(h[j]);
+                xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
+              }
+              y2[j] = __hfma2(xn, wh[j], bh[j]);
+              o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]));
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+              w8[i4 * 4 + h2 * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                                        (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmC, slab, c0, row0);      // rows beyond the matrix are clipped by the TMA unit
+          tma_store_2d(&tmC, slab + 4096u, c0 + 64, row0);
+          bulk_commit();
+        }
+        if (p.lno_x8 != nullptr) {
+          // the e4m3 copy leaves the same way: once the stores above have read the slab, its first 4 KB take the 32
+          // rows of 128 bytes (the same 128-byte swizzle), and one more TMA store follows
+          if (lane == 0) bulk_wait_read0();
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t off = slab + lane * 128 + ((q ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(w8[q * 4]), "r"(w8[q * 4 + 1]), "r"(w8[q * 4 + 2]), "r"(w8[q * 4 + 3]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmX8, slab, c0, row0);
+            bulk_commit();
+          }
+        }
+        if (exists(local + 2)) {
+          if (lane == 0) bulk_wait_read0();          // the stores have read the slab: the next residual slab may land
+          res_issue(local + 2);
+        }
+      }
+      if (!alive) {
+        if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
+        if (res_pending) mbar_wait(rbar, pending_ph);      // no copy into this CTA's memory stays in flight
+      }
+      if (lane == 0) bulk_wait_all();   // this warp's TMA stores have left shared memory and landed
+      __syncwarp();
+    } else if constexpr (PAIR) {
       // Slab epilogue. Per tile this warp owns rows [32*quarter, +32) x columns [64*part, +64) of the CTA's
       // accumulator half, drained in two TMEM loads of 32 columns; the accumulator buffer goes back to the MMA warp
       // as soon as the second load has landed in registers, before the arithmetic on it, and the finished slab
@@ -620,7 +865,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // two TMEM loads of 32 columns, each waited for before anything else touches its registers (a tcgen05.ld
         // fills them asynchronously); each half is then worked on as two pieces of 16 columns
         uint32_t acc[32];
-        float lsum = 0.0f, lsq = 0.0f;      // LNO: this lane's row, summed over the slab's 64 columns
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if ((i & 1) == 0) {
@@ -761,124 +1005,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t w0 = pack_f16x2(v[h2 * 8 + 0], v[h2 * 8 + 1]), w1 = pack_f16x2(v[h2 * 8 + 2], v[h2 * 8 + 3]);
               const uint32_t w2 = pack_f16x2(v[h2 * 8 + 4], v[h2 * 8 + 5]), w3 = pack_f16x2(v[h2 * 8 + 6], v[h2 * 8 + 7]);
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-              if constexpr (LNO) {
-                // statistics of the values as stored (rounded to f16), as a separate pass over the stored rows sees them
-                const uint32_t ws[4] = {w0, w1, w2, w3};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ws[j]));
-                  lsum += f.x + f.y;
-                  lsq = fmaf(f.x, f.x, fmaf(f.y, f.y, lsq));
-                }
-              }
-            }
-          }
-        }
-        if constexpr (LNO) {
-          // ---- LayerNorm over the whole output row. The slab holds y = acc + bias + residual as f16; this lane's row
-          // needs the sums of all N columns, which sit in 4 warps of each of the tiles_n CTAs that work on the row
-          // block's column tiles.
-          // (1) Inside the CTA: each warp leaves its partial in its own e4m3 slab buffer (unused until step 3; the
-          //     stores of the previous tile have read it); the last of the lane quarter's four warps to arrive adds
-          //     them in column order and publishes the CTA's record for these 32 rows.
-          const uint32_t slot8 = slot + 4096u;
-          asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(slot8 + 8u * lane), "f"(lsum), "f"(lsq) : "memory");
-          __syncwarp();
-          uint32_t old = 0;
-          if (lane == 0)
-            asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(ln_counter + 4u * quarter) : "memory");
-          old = __shfl_sync(0xffffffffu, old, 0);
-          const long long rec_row = (long long)rank * BM + quarter * 32 + lane;
-          if ((old & 3u) == 3u) {
-            float S = 0.0f, Q = 0.0f;
-#pragma unroll
-            for (int pp = 0; pp < 4; ++pp) {
-              // the warp with columns [64 pp, +64) of this lane quarter is epilogue warp 4 pp + ((quarter + 2) & 3)
-              const uint32_t src = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + uint32_t(4 * pp + ((quarter + 2) & 3)) * Cfg::SLOT_BYTES + 4096u + 8u * lane;
-              float a, b;
-              asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(src) : "memory");
-              S += a;
-              Q += b;
-            }
-            const unsigned long long pk = (static_cast<unsigned long long>(__float_as_uint(Q)) << 32) | __float_as_uint(S);
-            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.lno_stats + ((long long)mi * tiles_n + ni) * TM + rec_row), "l"(pk) : "memory");
-          }
-          // (2) Across the CTAs: poll the row's tiles_n records (each is valid as soon as it is not the preset
-          //     all-ones pattern: a record is one 8-byte store), bounded like every other wait.
-          float S = 0.0f, Q = 0.0f;
-          {
-            unsigned long long t0 = 0;
-            const unsigned long long* recs = p.lno_stats + (long long)mi * tiles_n * TM + rec_row;
-            for (int it = 0;; ++it) {
-              bool ok = true;
-              S = 0.0f; Q = 0.0f;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (j < tiles_n) {
-                  unsigned long long r;
-                  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(r) : "l"(recs + (long long)j * TM) : "memory");
-                  ok = ok && r != ~0ull;
-                  S += __uint_as_float(static_cast<uint32_t>(r));
-                  Q += __uint_as_float(static_cast<uint32_t>(r >> 32));
-                }
-              }
-              if (__all_sync(0xffffffffu, ok)) break;
-              if (it == 8) t0 = global_timer_ns();
-              if (it > 8) {
-                __nanosleep(64);
-                if (global_timer_ns() - t0 > 2000000000ull) {
-                  alive = false;
-                  break;
-                }
-              }
-            }
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) {
-              if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue);
-              break;
-            }
-          }
-          // (3) Normalise the slab in place (fp32 statistics, f16 affine: the arithmetic of the row kernels) and
-          //     derive the e4m3 copy.
-          const float inv_n = 1.0f / static_cast<float>(p.N);
-          const float mean = S * inv_n;
-          const float rstd = rsqrtf(fmaxf(Q * inv_n - mean * mean, 0.0f) + 1e-5f);
-          const float shift = -mean * rstd;
-          const __half2 s8 = __floats2half2_rn(p.lno_out8_scale, p.lno_out8_scale);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w8[4];
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-              const int q = i * 2 + h2;
-              const uint32_t off = slot + lane * 128 + ((q ^ (lane & 7)) << 4);
-              uint4 u;
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off) : "memory");
-              const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.lno_w16 + c0 + q * 8));
-              const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.lno_b16 + c0 + q * 8));
-              const __half2* h = reinterpret_cast<const __half2*>(&u);
-              const __half2* wh = reinterpret_cast<const __half2*>(&w4);
-              const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-              __half2 y2[4];
-              uint32_t o16[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h[j]);
-                const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
-                y2[j] = __hfma2(xn, wh[j], bh[j]);
-                o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
-              }
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]) : "memory");
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
-                w8[h2 * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
-                                 (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
-              }
-            }
-            if (p.lno_x8 != 0) {
-              const uint32_t off8 = slot8 + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off8), "r"(w8[0]), "r"(w8[1]), "r"(w8[2]), "r"(w8[3]) : "memory");
             }
           }
         }
@@ -887,9 +1013,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
           // rows and columns beyond the matrix are clipped by the TMA unit
           tma_store_2d(&tmC, slot, c0, m0 + quarter * 32);
-          if constexpr (LNO) {
-            if (p.lno_x8 != 0) tma_store_2d(&tmX8, slot + 4096u, c0, m0 + quarter * 32);
-          }
           bulk_commit();
         }
         if (RES != 0 && tma_res) {

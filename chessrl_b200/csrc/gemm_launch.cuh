@@ -58,7 +58,6 @@ inline int make_tmap_2d(CUtensorMap* out, const void* ptr, int esz, uint64_t inn
 }
 
 struct GemmArgs {
-  void* lno_x8 = nullptr;       // LNO kernels: [M, N] e4m3 copy of the normalised rows (nullable)
   int kind = kKindF16;          // MmaKind: element type of A and W
   const void* A = nullptr;      // [M, lda]
   long long lda = 0;            // elements
@@ -88,6 +87,8 @@ inline bool gemm_can_fuse_ln(long long M, int N, int K, int num_sms) {
 inline bool gemm_can_fuse_ln_out(long long M, int N, int num_sms) {
   return N % 256 == 0 && N <= 1024 && ((M + 255) / 256) * (N / 256) >= num_sms / 2;
 }
+// bytes of the exchange buffer: one 8-byte record per row (rounded up to whole 256-row blocks) and 128-column slab
+inline size_t gemm_ln_out_scratch_bytes(long long M) { return static_cast<size_t>((M + 255) / 256) * 8 * 256 * 8; }
 
 template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
@@ -127,16 +128,14 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       make_tmap_2d(&tmR, prm.residual, 2, prm.N, prm.M, static_cast<uint64_t>(prm.ldr) * 2, 32, 128) == kOk)
     prm.use_tma_res = 1;
   const int tiles = ((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN);
-  // LNO: the e4m3 copy of the normalised rows leaves through a tensor map of its own (pitch N)
+  // LNO: the e4m3 copy of the normalised rows leaves through a tensor map of its own (32 rows x 128 columns)
   CUtensorMap tmX8;
   std::memset(&tmX8, 0, sizeof(tmX8));
   if constexpr (LNO != 0) {
     if (!prm.use_tma_res || prm.lno_stats == nullptr || prm.lno_w16 == nullptr || prm.lno_b16 == nullptr) return kErrInvalid;
-    prm.lno_x8 = 0;
-    if (a.lno_x8 != nullptr) {
-      if (make_tmap_2d(&tmX8, a.lno_x8, 1, prm.N, prm.M, static_cast<uint64_t>(prm.N), 32, 64) != kOk) return kErrShape;
-      prm.lno_x8 = 1;
-    }
+    if (prm.lno_x8 != nullptr &&
+        make_tmap_2d(&tmX8, prm.lno_x8, 1, prm.N, prm.M, static_cast<uint64_t>(prm.N), 32, 128) != kOk)
+      return kErrShape;
   }
   if constexpr (PAIR) {
     // one 2-CTA cluster per pair of SMs (LNA: a pair owns whole row blocks, so no more pairs than row blocks)
@@ -167,7 +166,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       if (pairs > resident[dev]) pairs = resident[dev];
       cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
       // every record of the exchange buffer starts as the "not written yet" pattern
-      const size_t recs = static_cast<size_t>((a.p.M + Cfg::TM - 1) / Cfg::TM) * ((a.p.N + BN - 1) / BN) * Cfg::TM;
+      const size_t recs = gemm_ln_out_scratch_bytes(a.p.M) / sizeof(unsigned long long);
       if (cudaMemsetAsync(prm.lno_stats, 0xFF, recs * sizeof(unsigned long long), stream) != cudaSuccess) return kErrCuda;
     }
     return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, tmA, tmB, tmC, tmR, tmX8, prm) == cudaSuccess ? kOk : kErrCuda;
@@ -202,7 +201,8 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
                          (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
     if (KIND == kKindI8 || !gemm_can_fuse_ln_out(a.p.M, a.p.N, num_sms) || a.p.out_dtype != kOutF16 || !out_map_ok(a.p) ||
         !res_tma || a.p.col_scale != nullptr || a.p.row_scale != nullptr || a.p.ln_y != nullptr || a.p.lno_w16 == nullptr ||
-        a.p.lno_b16 == nullptr || (reinterpret_cast<uintptr_t>(a.p.lno_w16) & 15) != 0 ||
+        a.p.lno_b16 == nullptr || (reinterpret_cast<uintptr_t>(a.p.lno_w16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_x8) & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(a.p.bias) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
       return kErrUnsupported;
     if constexpr (KIND != kKindI8) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);

@@ -130,6 +130,11 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 
 // 2-D tiled store shared -> global (bulk async-group completion). Elements outside the tensor are
 // not written. Generic-proxy writes to the source tile need fence_proxy_async_smem() + a barrier first.
+// Hint: bring the box at (x, y) into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
                    reinterpret_cast<uint64_t>(tm)),

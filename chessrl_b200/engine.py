@@ -30,7 +30,7 @@ class EngineConfig:
     chunk: int = 0
     pos_embed: int = 0
     lm_vocab: int = 0
-    fuse_layernorm: int = L.FUSE_LN_OFF
+    fuse_layernorm: int = L.FUSE_LN_AUTO
     precision: int = 0
 
     @staticmethod

@@ -84,15 +84,17 @@ typedef struct crl_config {
   int32_t chunk;            /* positions processed per pass over the layers; 0 = library default */
   int32_t pos_embed;        /* 1: add the `pe` table [>=64, d] to the embedded tokens (model_bis.py:363-366) */
   int32_t lm_vocab;         /* CRL_POLICY_LM_HEAD: rows of lm_head.weight (1929 in the reference's scripts) */
-  int32_t fuse_layernorm;   /* CRL_FUSE_LN_OFF (0): the per-block LayerNorms are separate row passes; CRL_FUSE_LN_ON: large
-                               passes of post-LN networks run them inside the ff1 / QKV GEMM kernels (same bits; measured
-                               neither faster nor slower on B200, kept as an option); CRL_FUSE_LN_OUT: large FP16 / FP8
-                               passes of post-LN networks normalise inside the out-projection / ff2 GEMM kernels that
-                               produce the rows (x + sublayer(x) never crosses HBM; equal within f16 rounding) */
+  int32_t fuse_layernorm;   /* where the per-block LayerNorms of post-LN networks run. CRL_FUSE_LN_AUTO (0): the library
+                               chooses (CRL_FUSE_LN_OUT where it applies, separate row passes elsewhere); CRL_FUSE_LN_OUT:
+                               large FP16 / FP8 passes normalise inside the out-projection / ff2 GEMM kernels that produce
+                               the rows, so x + sublayer(x) never crosses HBM (equal to the separate passes within f16
+                               rounding; measured 4-5 % faster on B200); CRL_FUSE_LN_ON: inside the ff1 / QKV GEMM kernels
+                               that consume the rows (same bits as the separate passes, no measured gain);
+                               CRL_FUSE_LN_OFF: always separate row passes */
   int32_t precision;        /* bit mask of CRL_PREC_*; 0 = the fastest arithmetic of the chosen dtype */
 } crl_config;
 
-enum { CRL_FUSE_LN_OFF = 0, CRL_FUSE_LN_ON = 1, CRL_FUSE_LN_OUT = 2 };
+enum { CRL_FUSE_LN_AUTO = 0, CRL_FUSE_LN_ON = 1, CRL_FUSE_LN_OUT = 2, CRL_FUSE_LN_OFF = 3 };
 /* Precision switches. The FP8 engine (model_fp8.py:43-140: per-tensor e4m3 linears, everything else in higher
  * precision) takes several shortcuts around its e4m3 GEMMs by default; each bit takes one of them back, so that its
  * cost in accuracy and speed can be measured on its own:
@@ -258,7 +260,7 @@ typedef struct crl_linear_args {
    * lno_bias over the n columns (eps 1e-5: the post-LN block's norm1 / norm2 behind its out-projection / second FFN
    * linear, Leela/attn.py:478-486), computed inside the GEMM kernel; `residual` is required and may be `c` itself.
    * lno_weight / lno_bias are [n] f16; lno_x8 ([m, n] e4m3 of the rows times lno_out8_scale) is optional; lno_scratch
-   * is device memory of 8 * 256 * ceil(m / 256) * (n / 256) bytes the kernel exchanges row sums through. Needs f16 or
+   * is device memory of 16 KiB * ceil(m / 256) the kernel exchanges row sums through. Needs f16 or
    * e4m3 operands, an f16 output, n a multiple of 256 up to 1024 and at least half the SM count of 256 x 256 tiles;
    * CRL_ERR_UNSUPPORTED otherwise. */
   const void* lno_weight;

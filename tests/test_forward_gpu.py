@@ -714,6 +714,15 @@ def test_layernorm_inside_the_producing_gemm_matches_separate_passes(dtype, d):
         eng.close()
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert outs[0][2] == outs[2][2] - 2 * 3
+    if d == 512:      # large enough for the library to choose this route by itself
+        eng = Engine(EngineConfig(dtype=dtype, fuse_layernorm=crl.FUSE_LN_AUTO, **cfg.to_dict()))
+        eng.load_state_dict(sd)
+        if dtype == crl.DTYPE_F8E4M3:
+            eng.calibrate(planes[:256])
+        auto = eng.forward(planes, legal_mask=bits)
+        torch.cuda.synchronize()
+        assert torch.equal(auto["policy"].cpu(), outs[0][0]) and eng.last_launch_count() == outs[0][2]
+        eng.close()
     tol = 2e-3 if dtype == 0 else 2e-2           # FP8: a flipped f16 rounding can move an e4m3 rounding downstream
     assert (outs[0][0] - outs[2][0]).abs().max() <= tol and (outs[0][1] - outs[2][1]).abs().max() <= tol
     if dtype == 0:

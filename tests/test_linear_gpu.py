@@ -333,7 +333,7 @@ def test_layernorm_of_the_output_rows_inside_the_gemm(lib, kind, n, k, in_place,
     want = torch.nn.functional.layer_norm(pre, (n,), gamma.float(), beta.float(), 1e-5)
     c = res.clone() if in_place else torch.full((m + 2, n), 7.0, device="cuda", dtype=torch.float16)
     x8 = torch.full((m + 2, n), 0x55, device="cuda", dtype=torch.uint8)
-    scratch = torch.zeros(256 * ((m + 255) // 256) * (n // 256), device="cuda", dtype=torch.int64)
+    scratch = torch.zeros(2048 * ((m + 255) // 256), device="cuda", dtype=torch.int64)          # 16 KiB per 256 rows
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     x = L.LinearArgs()
     x.kind, x.out_dtype = kind, 0
@@ -375,7 +375,7 @@ def test_output_layernorm_is_refused_where_it_cannot_run(lib):
         w = torch.zeros(n, k, device="cuda", dtype=a.dtype)
         g = torch.ones(n, device="cuda", dtype=torch.float16)
         c = torch.full((m, n), 3.0, device="cuda", dtype=torch.float16)
-        scratch = torch.zeros(256 * ((m + 255) // 256) * ((n + 255) // 256), device="cuda", dtype=torch.int64)
+        scratch = torch.zeros(2048 * ((m + 255) // 256), device="cuda", dtype=torch.int64)
         x = L.LinearArgs()
         x.kind, x.out_dtype, x.a, x.lda, x.w, x.ldw, x.c, x.ldc = kind, 0, a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
         x.m, x.n, x.k, x.alpha, x.device_status = m, n, k, 1.0, status.data_ptr()
