@@ -610,9 +610,12 @@ def main():
     cpu, accuracy = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         n_acc = min(256, per_rank)
-        rows = eng.forward(planes[:n_acc], layout=layout, legal_mask=None if value_only else bits[:n_acc])
+        # the checked rows come out of a pass of the size the timed passes have (up to one chunk), so that they take
+        # the same kernels: small passes run the per-block LayerNorms as separate launches, large ones inside the GEMMs
+        n_pass = min(per_rank, 8192)
+        rows = eng.forward(planes[:n_pass], layout=layout, legal_mask=None if value_only else bits[:n_pass])
         torch.cuda.synchronize()
-        rows = {k: v.float().cpu() for k, v in rows.items()}
+        rows = {k: v[:n_acc].float().cpu() for k, v in rows.items()}
         sample = min(64 if d >= 1024 else 256, n_acc)
         cpu, accuracy = cpu_baseline_and_accuracy(wl, weights, value_only, pos, rows, sample=sample, steps=max(1, n_acc // sample))
 

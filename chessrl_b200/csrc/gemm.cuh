@@ -557,9 +557,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const __half2 s8 = __floats2half2_rn(p.lno_out8_scale, p.lno_out8_scale);
       const float inv_n = 1.0f / static_cast<float>(p.N);
       const float a_scale = p.alpha;
-      // with an e4m3 copy wanted (FP8 engine) the normalisation runs on packed f16 pairs: rstd and the shift rounded
-      // to f16 cost the f16 rows one more rounding, far below the e4m3 steps of everything that reads them
-      const bool packed = p.lno_x8 != nullptr && p.precise_act == 0;
       bool alive = true;
       int mi = 0, ni = 0;
       for (int local = set; tile_of(local, mi, ni); local += 2) {
@@ -690,7 +687,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const float rstd = rsqrtf(fmaxf(Q * inv_n - mean * mean, 0.0f) + 1e-5f);
         const float shift = -mean * rstd;
         const bool row_ok = row0 + lane < p.M;
-        const __half2 rstd2 = __floats2half2_rn(rstd, rstd), shift2 = __floats2half2_rn(shift, shift);
         uint32_t w8[32];      // the e4m3 copy of this lane's 128 columns
 #pragma unroll
         for (int i4 = 0; i4 < 8; ++i4) {
@@ -709,13 +705,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t o16[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              __half2 xn;
-              if (packed) {
-                xn = __hfma2(h[j], rstd2, shift2);
-              } else {
-                const float2 f = __half22float2(h[j]);
-                xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
-              }
+              const float2 f = __half22float2(h[j]);
+              const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
               y2[j] = __hfma2(xn, wh[j], bh[j]);
               o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
             }

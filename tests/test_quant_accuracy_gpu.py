@@ -48,11 +48,11 @@ def fake_quant(fmt):
 
 
 @functools.lru_cache(maxsize=None)
-def engine_out(dtype, precision=0):
+def engine_out(dtype, precision=0, fuse_layernorm=0):
     from chessrl_b200 import Engine, EngineConfig
     import chessrl_b200 as crl
     s = setup()
-    eng = Engine(EngineConfig(dtype=dtype, precision=precision, **s["cfg"].to_dict()))
+    eng = Engine(EngineConfig(dtype=dtype, precision=precision, fuse_layernorm=fuse_layernorm, **s["cfg"].to_dict()))
     eng.load_state_dict(s["sd"])
     x = s["pos"]["planes112"].cuda()
     if dtype == crl.DTYPE_F8E4M3:
@@ -160,6 +160,24 @@ def test_precision_switches_of_the_fp8_engine():
         assert m["wdl"] <= WDL_BAR_Q, label
         assert m["rms"] <= 1.15 * base["rms"], label
     assert rows[-1][1]["top1"] >= 0.98 and rows[-1][1]["rms"] <= 0.3 * base["rms"]
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_layernorm_inside_the_gemm_kernels_costs_no_accuracy(dtype):
+    """Large passes normalise inside the out-projection / ff2 kernels (CRL_FUSE_LN_OUT, the library's choice from a
+    few hundred positions on; forced here on the 256 test positions). Against the fp32 oracle both routes have to sit
+    at the same distance (the largest single error of an FP8 run moves by tens of per cent between any two variants
+    whose roundings differ somewhere, so it gets a wider band than the rms)."""
+    import chessrl_b200 as crl
+    s = setup()
+    sep = compare(*engine_out(dtype, 0, crl.FUSE_LN_OFF), s["ref_masked"], s["ref_wdl"], s["legal"])
+    fused = compare(*engine_out(dtype, 0, crl.FUSE_LN_OUT), s["ref_masked"], s["ref_wdl"], s["legal"])
+    for label, m in (("separate passes", sep), ("inside the GEMM kernels", fused)):
+        print(f"dtype {dtype}, LayerNorm {label:24s} top-1 {m['top1']:.4f}  logit max-abs {m['max_err']:.3e}  rms {m['rms']:.3e}  wdl {m['wdl']:.3e}")
+    assert fused["rms"] <= 1.1 * sep["rms"] + 1e-5 and fused["max_err"] <= 1.6 * sep["max_err"] + 1e-4
+    assert fused["wdl"] <= 1.3 * sep["wdl"] + 1e-4 and fused["top1"] >= sep["top1"] - 0.02
+    if dtype == 0:
+        assert fused["max_err"] <= LOGIT_BAR_F16 and fused["wdl"] <= WDL_BAR_F16
 
 
 @pytest.mark.parametrize("layers", [1, 2])
