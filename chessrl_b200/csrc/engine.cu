@@ -535,6 +535,7 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   // computed from.
   // (CRL_FUSE_LN_AUTO takes it from four tiles per CTA pair on: below that it measures neither faster nor slower.)
   const bool lno = !calib && !i8 && c.ln_mode == CRL_LN_POST && (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr &&
+                   c.ffn_act_pos == CRL_FFN_ACT_MID &&      // (no activation between the GEMM and the residual sum)
                    ((c.fuse_layernorm == CRL_FUSE_LN_OUT && gemm_can_fuse_ln_out(M, d, h->num_sms)) ||
                     (c.fuse_layernorm == CRL_FUSE_LN_AUTO && gemm_can_fuse_ln_out(M / 4, d, h->num_sms)));
 

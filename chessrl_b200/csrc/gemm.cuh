@@ -584,13 +584,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int row0 = mi * TM + rank * BM + quarter * 32;
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(set * BN + half * 128);
         uint32_t acc[32];
-        float lsum = 0.0f, lsq = 0.0f;
+        // (four independent partial sums each: one running sum would chain 128 dependent additions)
+        float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f}, pq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        auto chunk_off = [&](int k) {      // k-th 16-byte chunk (8 columns) of this lane's 128-column row
+          const int q = k & 7;
+          return slab + 4096u * (k >> 3) + lane * 128 + ((q ^ (lane & 7)) << 4);
+        };
+        uint4 rnext;      // the residual's next chunk, requested one chunk ahead of its use
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(0)));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if ((i & 1) == 0) {
-            tmem_ld_32x32(taddr + 16u * i, acc);
+        for (int k = 0; k < 16; ++k) {
+          if ((k & 3) == 0) {
+            tmem_ld_32x32(taddr + 8u * k, acc);
             tmem_ld_wait();
-            if (i == 6) {
+            if (k == 12) {
               // the last columns sit in registers: the accumulator buffer goes back to the MMA warp
               tc_fence_before();
               __syncwarp();
@@ -600,51 +607,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             }
           }
-          float v[16];
+          const uint4 u = rnext;
+          if (k + 1 < 16)
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(k + 1)));
+          float v[8];
           if (p.bias != nullptr) {
-            const float4* b4p = reinterpret_cast<const float4*>(p.bias + c0 + i * 16);
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 b4 = __ldg(b4p + q);
-              v[q * 4] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4]), a_scale, b4.x);
-              v[q * 4 + 1] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 1]), a_scale, b4.y);
-              v[q * 4 + 2] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 2]), a_scale, b4.z);
-              v[q * 4 + 3] = fmaf(__uint_as_float(acc[(i & 1) * 16 + q * 4 + 3]), a_scale, b4.w);
-            }
+            for (int j = 0; j < 8; ++j) v[j] = fmaf(__uint_as_float(acc[(k & 3) * 8 + j]), a_scale, bb[j]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(acc[(i & 1) * 16 + j]) * a_scale;
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[(k & 3) * 8 + j]) * a_scale;
           }
-          if (p.act == kActMish) {
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+          uint32_t ws[4];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = act_mish(v[j]);
-          } else if (p.act == kActGelu) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = act_gelu(v[j]);
-          } else if (p.act == kActRelu) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.0f);
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            const float y0 = v[2 * j] + f.x, y1 = v[2 * j + 1] + f.y;
+            ws[j] = pack_f16x2(y0, y1);
+            // row statistics from the fp32 sums (the stored f16 values differ from them by their rounding only)
+            ps[j] += y0 + y1;
+            pq[j] = fmaf(y0, y0, fmaf(y1, y1, pq[j]));
           }
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int q = (i & 3) * 2 + h2;      // 16-byte chunk of the sub-slab's 128-byte row
-            const uint32_t off = slab + 4096u * (i >> 2) + lane * 128 + ((q ^ (lane & 7)) << 4);
-            uint4 u;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off));
-            const __half2* h = reinterpret_cast<const __half2*>(&u);
-            uint32_t ws[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __half22float2(h[j]);
-              const float y0 = v[h2 * 8 + 2 * j] + f.x, y1 = v[h2 * 8 + 2 * j + 1] + f.y;
-              ws[j] = pack_f16x2(y0, y1);
-              // row statistics from the fp32 sums (the stored f16 values differ from them by their rounding only)
-              lsum += y0 + y1;
-              lsq = fmaf(y0, y0, fmaf(y1, y1, lsq));
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]));
-          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_off(k)), "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]));
         }
+        const float lsum = (ps[0] + ps[1]) + (ps[2] + ps[3]), lsq = (pq[0] + pq[1]) + (pq[2] + pq[3]);
         const unsigned long long* recs = p.lno_stats + (long long)mi * 8 * TM + rank * BM + quarter * 32 + lane;
         {
           const unsigned long long pk = (static_cast<unsigned long long>(__float_as_uint(lsq)) << 32) | __float_as_uint(lsum);
@@ -688,35 +678,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const float shift = -mean * rstd;
         const bool row_ok = row0 + lane < p.M;
         uint32_t w8[32];      // the e4m3 copy of this lane's 128 columns
+        uint4 ynext;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ynext.x), "=r"(ynext.y), "=r"(ynext.z), "=r"(ynext.w) : "r"(chunk_off(0)));
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
+        for (int k = 0; k < 16; ++k) {
+          const uint4 u = ynext;
+          if (k + 1 < 16)
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ynext.x), "=r"(ynext.y), "=r"(ynext.z), "=r"(ynext.w) : "r"(chunk_off(k + 1)));
+          const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.lno_w16 + c0 + k * 8));
+          const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.lno_b16 + c0 + k * 8));
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+          const __half2* wh = reinterpret_cast<const __half2*>(&w4);
+          const __half2* bh = reinterpret_cast<const __half2*>(&b4);
+          __half2 y2[4];
+          uint32_t o16[4];
 #pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int q = (i4 & 3) * 2 + h2;
-            const uint32_t off = slab + 4096u * (i4 >> 2) + lane * 128 + ((q ^ (lane & 7)) << 4);
-            uint4 u;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(off));
-            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.lno_w16 + c0 + i4 * 16 + h2 * 8));
-            const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.lno_b16 + c0 + i4 * 16 + h2 * 8));
-            const __half2* h = reinterpret_cast<const __half2*>(&u);
-            const __half2* wh = reinterpret_cast<const __half2*>(&w4);
-            const __half2* bh = reinterpret_cast<const __half2*>(&b4);
-            __half2 y2[4];
-            uint32_t o16[4];
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
+            y2[j] = __hfma2(xn, wh[j], bh[j]);
+            o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_off(k)), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __half22float2(h[j]);
-              const __half2 xn = __floats2half2_rn(fmaf(f.x, rstd, shift), fmaf(f.y, rstd, shift));
-              y2[j] = __hfma2(xn, wh[j], bh[j]);
-              o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(off), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]));
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
-              w8[i4 * 4 + h2 * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
-                                        (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
-            }
+          for (int j = 0; j < 2; ++j) {
+            const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+            w8[k * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                            (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
           }
         }
         fence_proxy_async_smem();

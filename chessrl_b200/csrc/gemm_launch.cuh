@@ -200,7 +200,7 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
     if (KIND == kKindI8 || !gemm_can_fuse_ln_out(a.p.M, a.p.N, num_sms) || a.p.out_dtype != kOutF16 || !out_map_ok(a.p) ||
-        !res_tma || a.p.col_scale != nullptr || a.p.row_scale != nullptr || a.p.ln_y != nullptr || a.p.lno_w16 == nullptr ||
+        !res_tma || a.p.col_scale != nullptr || a.p.row_scale != nullptr || a.p.ln_y != nullptr || a.p.lno_w16 == nullptr || a.p.act != kActNone ||
         a.p.lno_b16 == nullptr || (reinterpret_cast<uintptr_t>(a.p.lno_w16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_x8) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.bias) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
