@@ -592,47 +592,49 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         };
         uint4 rnext;      // the residual's next chunk, requested one chunk ahead of its use
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(0)));
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          if ((k & 3) == 0) {
-            tmem_ld_32x32(taddr + 8u * k, acc);
-            tmem_ld_wait();
-            if (k == 12) {
-              // the last columns sit in registers: the accumulator buffer goes back to the MMA warp
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) {
-                if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(set), 0));   // the leader's barrier
-                else mbar_arrive(tempty_bar(set));
-              }
+#pragma unroll 1
+        for (int g = 0; g < 4; ++g) {
+          tmem_ld_32x32(taddr + 32u * g, acc);
+          tmem_ld_wait();
+          if (g == 3) {
+            // the last columns sit in registers: the accumulator buffer goes back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (rank != 0) mbar_arrive_cluster(mapa_u32(tempty_bar(set), 0));   // the leader's barrier
+              else mbar_arrive(tempty_bar(set));
             }
           }
-          const uint4 u = rnext;
-          if (k + 1 < 16)
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(k + 1)));
-          float v[8];
-          if (p.bias != nullptr) {
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
-            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = fmaf(__uint_as_float(acc[(k & 3) * 8 + j]), a_scale, bb[j]);
-          } else {
+          for (int c = 0; c < 4; ++c) {
+            const int k = g * 4 + c;
+            const uint4 u = rnext;
+            if (k + 1 < 16)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(k + 1)));
+            float v[8];
+            if (p.bias != nullptr) {
+              const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
+              const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
+              const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[(k & 3) * 8 + j]) * a_scale;
+              for (int j = 0; j < 8; ++j) v[j] = fmaf(__uint_as_float(acc[c * 8 + j]), a_scale, bb[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[c * 8 + j]) * a_scale;
+            }
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+            uint32_t ws[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(h[j]);
+              const float y0 = v[2 * j] + f.x, y1 = v[2 * j + 1] + f.y;
+              ws[j] = pack_f16x2(y0, y1);
+              // row statistics from the fp32 sums (the stored f16 values differ from them by their rounding only)
+              ps[j] += y0 + y1;
+              pq[j] = fmaf(y0, y0, fmaf(y1, y1, pq[j]));
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_off(k)), "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]));
           }
-          const __half2* h = reinterpret_cast<const __half2*>(&u);
-          uint32_t ws[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(h[j]);
-            const float y0 = v[2 * j] + f.x, y1 = v[2 * j + 1] + f.y;
-            ws[j] = pack_f16x2(y0, y1);
-            // row statistics from the fp32 sums (the stored f16 values differ from them by their rounding only)
-            ps[j] += y0 + y1;
-            pq[j] = fmaf(y0, y0, fmaf(y1, y1, pq[j]));
-          }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_off(k)), "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]));
         }
         const float lsum = (ps[0] + ps[1]) + (ps[2] + ps[3]), lsq = (pq[0] + pq[1]) + (pq[2] + pq[3]);
         const unsigned long long* recs = p.lno_stats + (long long)mi * 8 * TM + rank * BM + quarter * 32 + lane;
