@@ -303,7 +303,7 @@ def gemm_case(kind, M, N, K, out, act=0, residual=0, launches=20):
         gamma = torch.ones(N, device=dev, dtype=torch.float16)
         beta = torch.zeros(N, device=dev, dtype=torch.float16)
         x8 = torch.empty(M, N, device=dev, dtype=torch.uint8)
-        scratch = torch.zeros(2048 * ((M + 255) // 256), device=dev, dtype=torch.int64)
+        scratch = torch.zeros(4096 * ((M + 255) // 256), device=dev, dtype=torch.int64)
         x = _lib.LinearArgs()
         x.kind, x.out_dtype = kind, 0
         x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), K, w.data_ptr(), K, r.data_ptr(), N

@@ -73,7 +73,7 @@ class LinearArgs(ctypes.Structure):
         ("ln_y", ctypes.c_void_p), ("ln_weight", ctypes.c_void_p), ("ln_bias", ctypes.c_void_p),
         ("ln_x", ctypes.c_void_p), ("ln_x8", ctypes.c_void_p), ("ln_out8_scale", ctypes.c_float),
         ("lno_weight", ctypes.c_void_p), ("lno_bias", ctypes.c_void_p), ("lno_x8", ctypes.c_void_p),
-        ("lno_out8_scale", ctypes.c_float), ("lno_scratch", ctypes.c_void_p),
+        ("lno_out8_scale", ctypes.c_float), ("lno_scratch", ctypes.c_void_p), ("lno_qscale", ctypes.c_void_p),
     ]
 
 

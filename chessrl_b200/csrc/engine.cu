@@ -302,7 +302,7 @@ Workspace carve(const crl_handle* h, char* base, int64_t bc, int64_t total) {
   w.v2q = reinterpret_cast<__half*>(take(static_cast<size_t>(bc) * 128 * 2));
   w.legal = reinterpret_cast<uint8_t*>(take(c.policy_mode == CRL_POLICY_GATHER1858 ? static_cast<size_t>(total) * 236 : 0));
   const bool lno = (c.fuse_layernorm == CRL_FUSE_LN_OUT || c.fuse_layernorm == CRL_FUSE_LN_AUTO) && c.ln_mode == CRL_LN_POST &&
-                   c.dtype != CRL_DTYPE_I8 && d % 256 == 0;
+                   d % 256 == 0;
   w.lno_stats = reinterpret_cast<unsigned long long*>(take(lno ? gemm_ln_out_scratch_bytes(static_cast<long long>(M)) : 0));
   w.total = off;
   return w;
@@ -345,6 +345,7 @@ struct Lin {
   // output LayerNorm: C = LN(acc + bias + residual) * w + b over the whole row, inside the GEMM kernel, with an optional
   // e4m3 copy (lno_x8) scaled by lno_out8_scale; lno_stats is the kernel's exchange buffer
   const __half* lno_w16 = nullptr; const __half* lno_b16 = nullptr; uint8_t* lno_x8 = nullptr; float lno_out8_scale = 1.0f;
+  float* lno_qscale = nullptr;      // int8 operands: per-token scales of the int8 copy in lno_x8
   unsigned long long* lno_stats = nullptr;
 };
 
@@ -360,7 +361,7 @@ int linear(crl_handle* h, const Lin& l, cudaStream_t s) {
   g.p.ln_y = l.ln_y; g.p.ln_ldy = l.k; g.p.ln_w16 = l.ln_w16; g.p.ln_b16 = l.ln_b16; g.p.ln_x = l.ln_x; g.p.ln_x8 = l.ln_x8;
   g.p.ln_out8_scale = l.ln_out8_scale; g.p.precise_act = l.precise_act;
   g.p.lno_w16 = l.lno_w16; g.p.lno_b16 = l.lno_b16; g.p.lno_stats = l.lno_stats; g.p.lno_out8_scale = l.lno_out8_scale;
-  g.p.lno_x8 = l.lno_x8;
+  g.p.lno_x8 = l.lno_x8; g.p.lno_qscale = l.lno_qscale;
   const size_t esz_in = l.kind == kKindF16 ? 2 : 1, esz_out = l.out == kOutF32 ? 4 : (l.out == kOutF16 ? 2 : 1);
   ProfScope ps(h, s, kCatGemm, 2.0 * l.m * l.n * l.k,
                static_cast<double>(l.m) * l.k * esz_in + static_cast<double>(l.n) * l.k * esz_in +
@@ -534,10 +535,13 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
   // never crosses HBM and the two row passes per block go away. The result lands in w.x, over the residual it was
   // computed from.
   // (CRL_FUSE_LN_AUTO takes it from four tiles per CTA pair on: below that it measures neither faster nor slower.)
-  const bool lno = !calib && !i8 && c.ln_mode == CRL_LN_POST && (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr &&
+  const bool lno = !calib && c.ln_mode == CRL_LN_POST && (prec & CRL_PREC_LN_F32) == 0 && w.lno_stats != nullptr &&
                    c.ffn_act_pos == CRL_FFN_ACT_MID &&      // (no activation between the GEMM and the residual sum)
                    ((c.fuse_layernorm == CRL_FUSE_LN_OUT && gemm_can_fuse_ln_out(M, d, h->num_sms)) ||
-                    (c.fuse_layernorm == CRL_FUSE_LN_AUTO && gemm_can_fuse_ln_out(M / 4, d, h->num_sms)));
+                    (c.fuse_layernorm == CRL_FUSE_LN_AUTO && !i8 && gemm_can_fuse_ln_out(M / 4, d, h->num_sms)));
+  // (The INT8 engine takes this route only when asked to: its per-token int8 copy needs a second exchange - the row
+  // maximum - and a third pass over the slab, and the longer GEMMs cost what the saved row passes gave: 63.0 against
+  // 63.5 ms per 4096 positions.)
 
   // ---- input planes -> token-major f16 rows ------------------------------------------------------
   {
@@ -673,8 +677,8 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       else if (i8) { o.kind = kKindI8; o.a = w.t2_8; o.w = L.wo_q; o.row_scale = w.t2s; o.col_scale = L.cs_o; }
       else { o.a = w.t2; o.w = L.wo; }
       if (lno) {
-        o.c = w.x; o.lno_w16 = L.ln1w16; o.lno_b16 = L.ln1b16; o.lno_x8 = f8 ? w.x8 : nullptr; o.lno_out8_scale = L.sa_ffn;
-        o.lno_stats = w.lno_stats;
+        o.c = w.x; o.lno_w16 = L.ln1w16; o.lno_b16 = L.ln1b16; o.lno_x8 = (f8 || i8) ? w.x8 : nullptr; o.lno_out8_scale = L.sa_ffn;
+        o.lno_qscale = i8 ? w.xs : nullptr; o.lno_stats = w.lno_stats;
       }
       if ((rc = linear(h, o, s)) != CRL_OK) return rc;
     }
@@ -711,9 +715,10 @@ int forward_chunk(crl_handle* h, const crl_io* io, int64_t b0, int64_t bc, const
       else if (i8) { b.kind = kKindI8; b.a = w.t1_8; b.w = L.wff2_q; b.row_scale = w.t1s; b.col_scale = L.cs_ff2; }
       else { b.a = w.t1; b.w = L.wff2; }
       if (lno) {
-        const bool emit8 = f8 && l + 1 < c.n_layers;
+        const bool emit8 = (f8 || i8) && l + 1 < c.n_layers;
         b.c = w.x; b.lno_w16 = L.ln2w16; b.lno_b16 = L.ln2b16; b.lno_x8 = emit8 ? w.x8 : nullptr;
-        b.lno_out8_scale = emit8 ? h->layers[l + 1].sa_in : 1.0f; b.lno_stats = w.lno_stats;
+        b.lno_out8_scale = (emit8 && f8) ? h->layers[l + 1].sa_in : 1.0f; b.lno_qscale = (emit8 && i8) ? w.xs : nullptr;
+        b.lno_stats = w.lno_stats;
       }
       if ((rc = linear(h, b, s)) != CRL_OK) return rc;
     }
@@ -1486,7 +1491,7 @@ int crl_linear_ex(const crl_linear_args* x) {
     if (x->lno_weight == nullptr || x->lno_bias == nullptr || x->lno_scratch == nullptr || x->residual == nullptr) return CRL_ERR_INVALID;
     g.p.lno_w16 = static_cast<const __half*>(x->lno_weight); g.p.lno_b16 = static_cast<const __half*>(x->lno_bias);
     g.p.lno_stats = static_cast<unsigned long long*>(x->lno_scratch); g.p.lno_out8_scale = x->lno_out8_scale;
-    g.p.lno_x8 = static_cast<uint8_t*>(x->lno_x8);
+    g.p.lno_x8 = static_cast<uint8_t*>(x->lno_x8); g.p.lno_qscale = x->lno_qscale;
   }
   return gemm_launch(g, sms, static_cast<cudaStream_t>(x->stream));
 }

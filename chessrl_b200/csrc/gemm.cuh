@@ -17,6 +17,7 @@
 // All waits are bounded (see ptx.cuh); a wait that runs out records a status code and unwinds.
 #pragma once
 #include <cuda_runtime.h>
+#include <type_traits>
 #include "ptx.cuh"
 
 namespace crl {
@@ -59,7 +60,8 @@ struct GemmParams {
   const __half* lno_w16;   // [N] f16 LayerNorm weight
   const __half* lno_b16;   // [N] f16 LayerNorm bias
   unsigned long long* lno_stats;   // [tiles_m][8 slabs][256 rows]
-  uint8_t* lno_x8;         // [M, N] e4m3 copy (nullable)
+  uint8_t* lno_x8;         // [M, N] e4m3 copy (nullable); int8 operands: the per-token int8 copy
+  float* lno_qscale;       // int8 operands: [M] per-token scales of the int8 copy (row maximum / 127), with lno_x8
   float lno_out8_scale;
 };
 
@@ -557,6 +559,39 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const __half2 s8 = __floats2half2_rn(p.lno_out8_scale, p.lno_out8_scale);
       const float inv_n = 1.0f / static_cast<float>(p.N);
       const float a_scale = p.alpha;
+      // Bounded wait for the `slabs` records of this lane's row; returns their sums (low and high word as floats), or
+      // the maximum of the low words.
+      auto poll_records = [&](const unsigned long long* recs, float& lo, float& hi, auto take_max) -> bool {
+        unsigned long long t0 = 0;
+        for (int it = 0;; ++it) {
+          bool ok = true;
+          unsigned long long r[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[j] = 0ull;
+            if (j < slabs) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(r[j]) : "l"(recs + (long long)j * TM) : "memory");
+          }
+          lo = 0.0f; hi = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            ok = ok && r[j] != ~0ull;
+            const float a = __uint_as_float(static_cast<uint32_t>(r[j]));
+            if constexpr (decltype(take_max)::value) {
+              lo = fmaxf(lo, a);
+            } else {
+              lo += a;
+              hi += __uint_as_float(static_cast<uint32_t>(r[j] >> 32));
+            }
+          }
+          if (__all_sync(0xffffffffu, ok)) return true;
+          if (it == 8) t0 = global_timer_ns();
+          if (it > 8) {
+            __nanosleep(64);
+            const bool late = global_timer_ns() - t0 > 2000000000ull;
+            if (__any_sync(0xffffffffu, late)) return false;
+          }
+        }
+      };
       bool alive = true;
       int mi = 0, ni = 0;
       for (int local = set; tile_of(local, mi, ni); local += 2) {
@@ -583,6 +618,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int c0 = ni * BN + half * 128;
         const int row0 = mi * TM + rank * BM + quarter * 32;
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(set * BN + half * 128);
+        float row_scale = a_scale;
+        if constexpr (KIND == kKindI8) {
+          if (p.row_scale != nullptr && row0 + lane < p.M) row_scale *= p.row_scale[row0 + lane];
+        }
         uint32_t acc[32];
         // (four independent partial sums each: one running sum would chain 128 dependent additions)
         float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f}, pq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -612,15 +651,34 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (k + 1 < 16)
               asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rnext.x), "=r"(rnext.y), "=r"(rnext.z), "=r"(rnext.w) : "r"(chunk_off(k + 1)));
             float v[8];
-            if (p.bias != nullptr) {
+            if constexpr (KIND == kKindI8) {
+              // int32 accumulators, alpha x the row's scale x the column scales
+              float sc[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sc[j] = row_scale;
+              if (p.col_scale != nullptr) {
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.col_scale + c0 + k * 8));
+                const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.col_scale + c0 + k * 8 + 4));
+                sc[0] *= s0.x; sc[1] *= s0.y; sc[2] *= s0.z; sc[3] *= s0.w;
+                sc[4] *= s1.x; sc[5] *= s1.y; sc[6] *= s1.z; sc[7] *= s1.w;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = static_cast<float>(static_cast<int>(acc[c * 8 + j])) * sc[j];
+              if (p.bias != nullptr) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              }
+            } else if (p.bias != nullptr) {
               const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
               const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
               const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = fmaf(__uint_as_float(acc[c * 8 + j]), a_scale, bb[j]);
+              for (int j = 0; j < 8; ++j) v[j] = fmaf(__uint_as_float(acc[c * 8 + j]), row_scale, bb[j]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[c * 8 + j]) * a_scale;
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[c * 8 + j]) * row_scale;
             }
             const __half2* h = reinterpret_cast<const __half2*>(&u);
             uint32_t ws[4];
@@ -645,41 +703,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // the row's records (each is valid as soon as it is not the preset all-ones pattern: a record is one 8-byte
         // store), added in a fixed order: a row's result does not depend on who computes it
         float S = 0.0f, Q = 0.0f;
-        {
-          unsigned long long t0 = 0;
-          for (int it = 0;; ++it) {
-            bool ok = true;
-            unsigned long long r[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              r[j] = 0ull;
-              if (j < slabs) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(r[j]) : "l"(recs + (long long)j * TM) : "memory");
-            }
-            S = 0.0f; Q = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              ok = ok && r[j] != ~0ull;
-              S += __uint_as_float(static_cast<uint32_t>(r[j]));
-              Q += __uint_as_float(static_cast<uint32_t>(r[j] >> 32));
-            }
-            if (__all_sync(0xffffffffu, ok)) break;
-            if (it == 8) t0 = global_timer_ns();
-            if (it > 8) {
-              __nanosleep(64);
-              const bool late = global_timer_ns() - t0 > 2000000000ull;
-              if (__any_sync(0xffffffffu, late)) {
-                alive = false;
-                break;
-              }
-            }
-          }
-          if (!alive) break;
+        if (!poll_records(recs, S, Q, std::false_type{})) {
+          alive = false;
+          break;
         }
         const float mean = S * inv_n;
         const float rstd = rsqrtf(fmaxf(Q * inv_n - mean * mean, 0.0f) + 1e-5f);
         const float shift = -mean * rstd;
         const bool row_ok = row0 + lane < p.M;
-        uint32_t w8[32];      // the e4m3 copy of this lane's 128 columns
+        uint32_t w8[32];      // the e4m3 (int8) copy of this lane's 128 columns
+        __half2 m2 = __float2half2_rn(0.0f);      // int8: largest |x'| of this lane's 128 columns
         uint4 ynext;
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ynext.x), "=r"(ynext.y), "=r"(ynext.z), "=r"(ynext.w) : "r"(chunk_off(0)));
 #pragma unroll
@@ -702,11 +735,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             o16[j] = *reinterpret_cast<const uint32_t*>(&y2[j]);
           }
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk_off(k)), "r"(o16[0]), "r"(o16[1]), "r"(o16[2]), "r"(o16[3]));
+          if constexpr (KIND == kKindI8) {
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
-            w8[k * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
-                            (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+            for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(y2[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
+              w8[k * 2 + j] = uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&a), __NV_SATFINITE, __NV_E4M3)) |
+                              (uint32_t(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&b), __NV_SATFINITE, __NV_E4M3)) << 16);
+            }
           }
         }
         fence_proxy_async_smem();
@@ -715,6 +753,38 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_store_2d(&tmC, slab, c0, row0);      // rows beyond the matrix are clipped by the TMA unit
           tma_store_2d(&tmC, slab + 4096u, c0 + 64, row0);
           bulk_commit();
+        }
+        if constexpr (KIND == kKindI8) {
+          if (p.lno_qscale != nullptr) {
+            // per-token int8 copy: the largest |x'| of the whole row, exchanged like the sums (second half of the
+            // record buffer), then the slab's values quantised with the row's scale
+            const unsigned long long* arecs = recs + (long long)tiles_m * 8 * TM;
+            const unsigned long long pk = __float_as_uint(fmaxf(__low2float(m2), __high2float(m2)));
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(arecs + (long long)(ni * 2 + half) * TM), "l"(pk) : "memory");
+            float amax = 0.0f, unused = 0.0f;
+            if (!poll_records(arecs, amax, unused, std::true_type{})) {
+              alive = false;
+              break;
+            }
+            const float qs = amax > 0.0f ? amax / 127.0f : 1.0f;
+            const float qinv = 1.0f / qs;
+            if (ni == 0 && half == 0 && row_ok) p.lno_qscale[row0 + lane] = qs;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              uint4 u;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(chunk_off(k)));
+              const __half2* h = reinterpret_cast<const __half2*>(&u);
+              uint32_t b8[8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                b8[2 * j] = static_cast<uint32_t>(max(-127, min(127, __float2int_rn(f.x * qinv)))) & 0xffu;
+                b8[2 * j + 1] = static_cast<uint32_t>(max(-127, min(127, __float2int_rn(f.y * qinv)))) & 0xffu;
+              }
+              w8[k * 2] = b8[0] | (b8[1] << 8) | (b8[2] << 16) | (b8[3] << 24);
+              w8[k * 2 + 1] = b8[4] | (b8[5] << 8) | (b8[6] << 16) | (b8[7] << 24);
+            }
+          }
         }
         if (p.lno_x8 != nullptr) {
           // the e4m3 copy leaves the same way: once the stores above have read the slab, its first 4 KB take the 32

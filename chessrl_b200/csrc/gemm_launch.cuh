@@ -87,8 +87,9 @@ inline bool gemm_can_fuse_ln(long long M, int N, int K, int num_sms) {
 inline bool gemm_can_fuse_ln_out(long long M, int N, int num_sms) {
   return N % 256 == 0 && N <= 1024 && ((M + 255) / 256) * (N / 256) >= num_sms / 2;
 }
-// bytes of the exchange buffer: one 8-byte record per row (rounded up to whole 256-row blocks) and 128-column slab
-inline size_t gemm_ln_out_scratch_bytes(long long M) { return static_cast<size_t>((M + 255) / 256) * 8 * 256 * 8; }
+// bytes of the exchange buffer: one 8-byte record per row (rounded up to whole 256-row blocks) and 128-column slab for
+// the sums, and as many again for the row maxima of the int8 copy
+inline size_t gemm_ln_out_scratch_bytes(long long M) { return static_cast<size_t>((M + 255) / 256) * 2 * 8 * 256 * 8; }
 
 template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
@@ -196,16 +197,22 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     }
   }
   if (a.p.lno_stats != nullptr) {
-    // output rows normalised inside the kernel: the residual kernel of CTA pairs, f16 / e4m3 operands
+    // output rows normalised inside the kernel: the residual kernel of CTA pairs. int8 operands may carry per-token
+    // and per-channel scales and ask for a per-token int8 copy (lno_x8 with lno_qscale); f16 / e4m3 operands for an
+    // e4m3 copy (lno_x8 alone)
     const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
-    if (KIND == kKindI8 || !gemm_can_fuse_ln_out(a.p.M, a.p.N, num_sms) || a.p.out_dtype != kOutF16 || !out_map_ok(a.p) ||
-        !res_tma || a.p.col_scale != nullptr || a.p.row_scale != nullptr || a.p.ln_y != nullptr || a.p.lno_w16 == nullptr || a.p.act != kActNone ||
+    const bool scales_ok = KIND == kKindI8 ? ((reinterpret_cast<uintptr_t>(a.p.col_scale) & 15) == 0 &&
+                                              (a.p.lno_qscale == nullptr || a.p.lno_x8 != nullptr))
+                                           : (a.p.col_scale == nullptr && a.p.row_scale == nullptr && a.p.lno_qscale == nullptr);
+    if (!gemm_can_fuse_ln_out(a.p.M, a.p.N, num_sms) || a.p.out_dtype != kOutF16 || !out_map_ok(a.p) || !res_tma || !scales_ok ||
+        (KIND == kKindI8 && a.p.lno_x8 != nullptr && a.p.lno_qscale == nullptr) ||
+        a.p.ln_y != nullptr || a.p.lno_w16 == nullptr || a.p.act != kActNone ||
         a.p.lno_b16 == nullptr || (reinterpret_cast<uintptr_t>(a.p.lno_w16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_x8) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.bias) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
       return kErrUnsupported;
-    if constexpr (KIND != kKindI8) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);
+    return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);
   }
   // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&

@@ -86,9 +86,9 @@ typedef struct crl_config {
   int32_t lm_vocab;         /* CRL_POLICY_LM_HEAD: rows of lm_head.weight (1929 in the reference's scripts) */
   int32_t fuse_layernorm;   /* where the per-block LayerNorms of post-LN networks run. CRL_FUSE_LN_AUTO (0): the library
                                chooses (CRL_FUSE_LN_OUT where it applies, separate row passes elsewhere); CRL_FUSE_LN_OUT:
-                               large FP16 / FP8 passes normalise inside the out-projection / ff2 GEMM kernels that produce
-                               the rows, so x + sublayer(x) never crosses HBM (equal to the separate passes within f16
-                               rounding; measured 4-5 % faster on B200); CRL_FUSE_LN_ON: inside the ff1 / QKV GEMM kernels
+                               large passes normalise inside the out-projection / ff2 GEMM kernels that produce the rows,
+                               so x + sublayer(x) never crosses HBM (equal to the separate passes within f16 rounding;
+                               measured 4-6 % faster on B200 for FP16 / FP8, which is where AUTO uses it; no gain for INT8); CRL_FUSE_LN_ON: inside the ff1 / QKV GEMM kernels
                                that consume the rows (same bits as the separate passes, no measured gain);
                                CRL_FUSE_LN_OFF: always separate row passes */
   int32_t precision;        /* bit mask of CRL_PREC_*; 0 = the fastest arithmetic of the chosen dtype */
@@ -260,14 +260,16 @@ typedef struct crl_linear_args {
    * lno_bias over the n columns (eps 1e-5: the post-LN block's norm1 / norm2 behind its out-projection / second FFN
    * linear, Leela/attn.py:478-486), computed inside the GEMM kernel; `residual` is required and may be `c` itself.
    * lno_weight / lno_bias are [n] f16; lno_x8 ([m, n] e4m3 of the rows times lno_out8_scale) is optional; lno_scratch
-   * is device memory of 16 KiB * ceil(m / 256) the kernel exchanges row sums through. Needs f16 or
-   * e4m3 operands, an f16 output, n a multiple of 256 up to 1024 and at least half the SM count of 256 x 256 tiles;
+   * is device memory of 32 KiB * ceil(m / 256) the kernel exchanges row sums through. Needs an
+   * f16 output, n a multiple of 256 up to 1024 and at least half the SM count of 256 x 256 tiles;
    * CRL_ERR_UNSUPPORTED otherwise. */
   const void* lno_weight;
   const void* lno_bias;
   void* lno_x8;
   float lno_out8_scale;
   void* lno_scratch;
+  float* lno_qscale;       /* int8 operands only: lno_x8 receives the per-token int8 copy of the rows (W8A8 activations:
+                              row maximum / 127 as the scale, written here, [m] f32); required with lno_x8 then */
 } crl_linear_args;
 int crl_linear_ex(const crl_linear_args* args);
 

@@ -333,7 +333,7 @@ def test_layernorm_of_the_output_rows_inside_the_gemm(lib, kind, n, k, in_place,
     want = torch.nn.functional.layer_norm(pre, (n,), gamma.float(), beta.float(), 1e-5)
     c = res.clone() if in_place else torch.full((m + 2, n), 7.0, device="cuda", dtype=torch.float16)
     x8 = torch.full((m + 2, n), 0x55, device="cuda", dtype=torch.uint8)
-    scratch = torch.zeros(2048 * ((m + 255) // 256), device="cuda", dtype=torch.int64)          # 16 KiB per 256 rows
+    scratch = torch.zeros(4096 * ((m + 255) // 256), device="cuda", dtype=torch.int64)          # 32 KiB per 256 rows
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     x = L.LinearArgs()
     x.kind, x.out_dtype = kind, 0
@@ -364,6 +364,62 @@ def test_layernorm_of_the_output_rows_inside_the_gemm(lib, kind, n, k, in_place,
         assert bool((x8 == 0x55).all())
 
 
+@pytest.mark.parametrize("k,want_copy", [(1024, True), (1536, True), (1024, False)])
+def test_layernorm_of_the_output_rows_with_int8_operands(lib, k, want_copy):
+    """LNO kernels on int8 operands (per-token and per-channel scales in, W8A8): the normalised rows in f16 and their
+    per-token int8 copy - scale = row maximum / 127, exchanged between the CTAs that hold the row's column tiles -
+    as the stand-alone LayerNorm kernel of the INT8 engine writes them. The copy and the scales are checked
+    against the f16 rows the kernel wrote (the int8 values up to the rounding of the reciprocal scale)."""
+    import ctypes
+    from chessrl_b200 import _lib as L
+    torch.manual_seed(k + int(want_copy))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    m, n = 256 * (sms // 4 + 9) + 77, 1024
+    a = torch.randint(-127, 128, (m, k), device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8)
+    rs = (torch.rand(m, device="cuda") * 0.02 + 0.005)
+    cs = (torch.rand(n, device="cuda") * 0.02 + 0.005) / 40.0
+    bias = torch.randn(n, device="cuda")
+    res = (torch.randn(m, n, device="cuda") * 1.5 + 0.3).half()
+    gamma = (1.0 + 0.1 * torch.randn(n, device="cuda")).half()
+    beta = (0.1 * torch.randn(n, device="cuda")).half()
+    acc = (a.double() @ w.double().t()).float()                      # exact: |sums| < 2^53
+    pre = (acc * rs[:, None] * cs[None, :] + bias + res.float()).half().float()
+    want = torch.nn.functional.layer_norm(pre, (n,), gamma.float(), beta.float(), 1e-5)
+    c = res.clone()
+    q8 = torch.full((m + 2, n), 0x55, device="cuda", dtype=torch.int8)
+    qs = torch.full((m + 2,), -1.0, device="cuda")
+    scratch = torch.zeros(4096 * ((m + 255) // 256), device="cuda", dtype=torch.int64)          # 32 KiB per 256 rows
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    x = L.LinearArgs()
+    x.kind, x.out_dtype = 2, 0
+    x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
+    x.m, x.n, x.k = m, n, k
+    x.bias, x.residual, x.ldr = bias.data_ptr(), c.data_ptr(), n
+    x.alpha, x.out_scale = 1.0, 1.0
+    x.row_scale, x.col_scale = rs.data_ptr(), cs.data_ptr()
+    x.device_status = status.data_ptr()
+    x.lno_weight, x.lno_bias, x.lno_scratch = gamma.data_ptr(), beta.data_ptr(), scratch.data_ptr()
+    if want_copy:
+        x.lno_x8, x.lno_qscale = q8.data_ptr(), qs.data_ptr()
+    rc = lib.crl_linear_ex(ctypes.byref(x))
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status[0]) == 0, (rc, int(status[0]))
+    got = c.float()
+    assert_close_elementwise(got, want, 6e-3 + 2e-3 * want.abs())
+    assert (got - want).abs().mean().item() < 6e-4
+    if want_copy:
+        amax = got.abs().amax(dim=1)
+        want_qs = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+        assert torch.allclose(qs[:m], want_qs, rtol=1e-6, atol=0.0) and bool((qs[m:] == -1.0).all())
+        want_q = torch.round(got * (1.0 / qs[:m])[:, None]).clamp(-127, 127)
+        dq = (q8[:m].float() - want_q).abs()         # a product within a rounding error of .5 may land on either side
+        assert dq.max().item() <= 1 and (dq > 0).float().mean().item() < 1e-4
+        assert bool((q8[m:] == 0x55).all()), "int8 rows beyond M were written"
+    else:
+        assert bool((q8 == 0x55).all()) and bool((qs == -1.0).all())
+
+
 def test_output_layernorm_is_refused_where_it_cannot_run(lib):
     """Too few tiles for the CTA pairs, a width that is no multiple of 256, int8 operands: CRL_ERR_UNSUPPORTED."""
     import ctypes
@@ -375,12 +431,14 @@ def test_output_layernorm_is_refused_where_it_cannot_run(lib):
         w = torch.zeros(n, k, device="cuda", dtype=a.dtype)
         g = torch.ones(n, device="cuda", dtype=torch.float16)
         c = torch.full((m, n), 3.0, device="cuda", dtype=torch.float16)
-        scratch = torch.zeros(2048 * ((m + 255) // 256), device="cuda", dtype=torch.int64)
+        scratch = torch.zeros(4096 * ((m + 255) // 256), device="cuda", dtype=torch.int64)
         x = L.LinearArgs()
         x.kind, x.out_dtype, x.a, x.lda, x.w, x.ldw, x.c, x.ldc = kind, 0, a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
         x.m, x.n, x.k, x.alpha, x.device_status = m, n, k, 1.0, status.data_ptr()
         x.residual, x.ldr = c.data_ptr(), n
         x.lno_weight, x.lno_bias, x.lno_scratch = g.data_ptr(), g.data_ptr(), scratch.data_ptr()
+        if kind == 2:
+            x.lno_x8 = a.data_ptr()          # int8 copy asked for, lno_qscale missing
         assert lib.crl_linear_ex(ctypes.byref(x)) == -8, (kind, m, n)
         torch.cuda.synchronize()
         assert bool((c == 3.0).all())
