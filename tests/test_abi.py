@@ -24,3 +24,37 @@ def test_argument_errors_without_gpu(lib):
     st = ctypes.c_int(0)
     assert lib.crl_last_status(None, ctypes.byref(st)) == -1
     assert lib.crl_linear(7, None, 0, None, 0, None, 0, 0, 1, 1, 1, None, None, 0, 1.0, 0, None, None) == -1
+
+
+def test_ctypes_mirrors_match_the_header_layout(tmp_path):
+    """The Python side passes crl_config / crl_io / crl_linear_args by pointer: size and the offset of every field of
+    the ctypes mirrors must be what a C compiler makes of the header (a field added on one side only would shift
+    everything behind it without any error)."""
+    import ctypes
+    import shutil
+    import subprocess
+    import pytest
+    from chessrl_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    mirrors = {"crl_config": _lib.Config, "crl_io": _lib.IO, "crl_linear_args": _lib.LinearArgs}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "chessrl_b200.h"', 'int main(void) {']
+    for cname, cls in mirrors.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    want = {}
+    for line in out.splitlines():
+        cname, fname, value = line.split()
+        want[(cname, fname)] = int(value)
+    for cname, cls in mirrors.items():
+        assert ctypes.sizeof(cls) == want[(cname, "size")], cname
+        for fname, _ in cls._fields_:
+            assert getattr(cls, fname).offset == want[(cname, fname)], (cname, fname)
