@@ -59,7 +59,7 @@ struct GemmParams {
   // copy * lno_out8_scale to lno_x8.
   const __half* lno_w16;   // [N] f16 LayerNorm weight
   const __half* lno_b16;   // [N] f16 LayerNorm bias
-  unsigned long long* lno_stats;   // [tiles_m][8 slabs][256 rows]
+  unsigned long long* lno_stats;   // [2][tiles_m][8 slabs][256 rows]: sums; row maxima (int8 copy)
   uint8_t* lno_x8;         // [M, N] e4m3 copy (nullable); int8 operands: the per-token int8 copy
   float* lno_qscale;       // int8 operands: [M] per-token scales of the int8 copy (row maximum / 127), with lno_x8
   float lno_out8_scale;
@@ -105,7 +105,7 @@ struct GemmCfg {
   static constexpr uint32_t SLOT_BYTES = PAIR ? (O8 ? 2048 : (LNO ? 8192 : 4096)) : 2048;
   // pairs: f16 slabs leave room for five 32 KB stages (four with the int8 scale table)
   // pairs: five 32 KB stages; the f16-output kernels with a fused LayerNorm give one up for its parameter table
-  // (LNO kernels keep three: their second slab per warp takes the room of two)
+  // (LNO kernels keep three: their 8 KB slabs take the room of two)
   static constexpr int STAGES = PAIR ? (LNO ? 3 : ((LNA && !O8) ? 4 : ((O8 && KIND != kKindI8) ? CRL_PAIR_O8_STAGES : 5)))
                                      : ((BN == 256) ? 3 : (BN == 128 ? 5 : 6));
   static constexpr uint32_t LN_PRM_BYTES = LNA ? 4096 : 0;    // LayerNorm weight [1024] and bias [1024] as f16
@@ -120,7 +120,7 @@ struct GemmCfg {
   static_assert(2 * STAGES + 4 <= 16, "the ring and accumulator barriers share 128 bytes");
   static constexpr uint32_t TMEM_SLOT_OFF = BAR_OFF + 128;
   static constexpr uint32_t RBAR_OFF = BAR_OFF + 144;
-  static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 16;     // (two per warp: LNO kernels have two slabs)
+  static constexpr uint32_t LN_COUNTER_OFF = RBAR_OFF + kEpiWarps * 16;     // (room for two mbarriers per warp; one is used)
   static constexpr uint32_t USED_BYTES = LN_COUNTER_OFF + 48;   // [0] epilogue warps' arrivals, [4 + w] blocks done by LayerNorm warp w
   static constexpr size_t SMEM_BYTES = size_t(USED_BYTES) + ((PAIR && (!O8 || STAGES > 5)) ? 496 : 896) /*alignment slack*/;
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");

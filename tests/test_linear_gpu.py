@@ -307,7 +307,7 @@ def test_layernorm_fusion_is_refused_where_it_cannot_run(lib):
 
 @pytest.mark.parametrize("kind,n,k,in_place,want8", [(1, 1024, 1024, True, True), (1, 1024, 1536, True, True),
                                                      (0, 1024, 1024, False, False), (1, 512, 1024, False, True),
-                                                     (0, 256, 512, True, True)])
+                                                     (0, 256, 512, True, True), (1, 768, 768, True, True)])
 def test_layernorm_of_the_output_rows_inside_the_gemm(lib, kind, n, k, in_place, want8):
     """LNO kernels: c = LayerNorm(a @ w.T * alpha + bias + residual) over the n columns, the row sums exchanged between
     the CTAs that hold the row block's column tiles. Checked against torch on the GPU: the pre-norm sum in fp32 from
