@@ -324,7 +324,10 @@ __device__ __forceinline__ bool ln_wait_blocks(uint32_t words_smem, uint32_t blo
   }
 }
 
-template <int BN, int KIND, int PAIR, int RES, int O8, int LNA, int LNO = 0>
+// EPI != 0 (CTA pairs with an e4m3 output, no residual, no column scales, N a multiple of 64): the epilogue's switches
+// are fixed at compile time - 1: bias, no activation; 2: no bias, no activation; 3: bias and Mish on packed f16 pairs -
+// which takes their tests and the untaken paths out of the three hottest instantiations. Same arithmetic as EPI = 0.
+template <int BN, int KIND, int PAIR, int RES, int O8, int LNA, int LNO = 0, int EPI = 0>
 __global__ void __launch_bounds__(kGemmThreads + (LNA ? 32 * kLnWarps : 0), 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
@@ -842,7 +845,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       };
       const bool tma_res = RES != 0 && p.use_tma_res != 0 && p.residual != nullptr;
       if (RES != 0 && tma_res && res_wanted(0)) res_issue(0);
-      const bool mish8 = O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0;
+      constexpr bool kSpec = EPI != 0;
+      static_assert(!kSpec || (O8 != 0 && RES == 0 && KIND != kKindI8), "specialised epilogues: e4m3 output, no residual, no column scales");
+      const bool has_bias = kSpec ? (EPI != 2) : (p.bias != nullptr);
+      const int act = kSpec ? (EPI == 3 ? kActMish : kActNone) : p.act;
+      const bool mish8 = kSpec ? (EPI == 3) : (O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0);
       if constexpr (LNA) {
         // the worker's first row block: nothing to drain yet, so the epilogue warps normalise rows too
         if (worker < tiles_m) {
@@ -891,7 +898,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
         // e4m3 output without an activation or residual: out = (alpha acc + bias) s = (alpha s) acc + (bias s), one
         // multiply-add per element instead of three operations
-        const bool fold = O8 != 0 && p.act == kActNone && p.residual == nullptr;
+        const bool fold = kSpec ? (EPI != 3) : (O8 != 0 && p.act == kActNone && p.residual == nullptr);
         const float os = fold ? 1.0f : p.out_scale;
         const float bs = fold ? p.out_scale : 1.0f;
         const float a_scale = p.alpha * rs * bs;
@@ -908,10 +915,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (lane == 0) bulk_wait_read0();
           __syncwarp();
         }
-        const bool direct_res = p.residual != nullptr && !(RES != 0 && tma_res) && row_ok;
+        const bool direct_res = kSpec ? false : (p.residual != nullptr && !(RES != 0 && tma_res) && row_ok);
         // bias and per-column scales: 16 floats per piece, the same addresses for every lane (one L1 transaction each)
-        const bool tab_vec = c0 + 64 <= p.N && (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
-                             (p.col_scale == nullptr || (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0);
+        const bool tab_vec = kSpec ? true
+                                   : (c0 + 64 <= p.N && (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+                                      (p.col_scale == nullptr || (reinterpret_cast<uintptr_t>(p.col_scale) & 15) == 0));
         const bool res_vec = (p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
         // two TMEM loads of 32 columns, each waited for before anything else touches its registers (a tcgen05.ld
         // fills them asynchronously); each half is then worked on as two pieces of 16 columns
@@ -956,7 +964,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           // v = raw * sc + bias * bs: one multiply-add per element when bs is 1 (no folded output scale)
           float bv[16];
-          if (p.bias != nullptr) {
+          if (has_bias) {
             if (tab_vec) {
               const float4* b4p = reinterpret_cast<const float4*>(p.bias + c0 + i * 16);
 #pragma unroll
@@ -982,13 +990,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           // activation: the switch sits outside the element loop so that the independent evaluations interleave;
           // Mish into an e4m3 output runs on packed f16 pairs at the conversion below
           if (mish8) {
-          } else if (p.act == kActMish) {
+          } else if (act == kActMish) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = act_mish(v[j]);
-          } else if (p.act == kActGelu) {
+          } else if (act == kActGelu) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = act_gelu(v[j]);
-          } else if (p.act == kActRelu) {
+          } else if (act == kActRelu) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.0f);
           }

@@ -91,14 +91,14 @@ inline bool gemm_can_fuse_ln_out(long long M, int N, int num_sms) {
 // the sums, and as many again for the row maxima of the int8 copy
 inline size_t gemm_ln_out_scratch_bytes(long long M) { return static_cast<size_t>((M + 255) / 256) * 2 * 8 * 256 * 8; }
 
-template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0>
+template <int BN, int KIND, int PAIR = 0, int RES = 0, int O8 = 0, int LNA = 0, int LNO = 0, int EPI = 0>
 inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, KIND, PAIR, RES, O8, LNA, LNO>;
   static bool attr_set[64] = {};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return kErrCuda;
     attr_set[dev] = true;
@@ -159,7 +159,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       if (resident[dev] == 0) {
         int n = 0;
         cfg.gridDim = dim3(static_cast<unsigned>(2 * (num_sms / 2)));
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, &cfg) != cudaSuccess || n <= 0)
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO, EPI>, &cfg) != cudaSuccess || n <= 0)
           return kErrCuda;
         resident[dev] = n;
         if (std::getenv("CRL_DEBUG") != nullptr) std::fprintf(stderr, "chessrl_b200: %d CTA pairs resident at once on device %d\n", n, dev);
@@ -170,7 +170,7 @@ inline int gemm_launch_t(const GemmArgs& a, int num_sms, cudaStream_t stream) {
       const size_t recs = gemm_ln_out_scratch_bytes(a.p.M) / sizeof(unsigned long long);
       if (cudaMemsetAsync(prm.lno_stats, 0xFF, recs * sizeof(unsigned long long), stream) != cudaSuccess) return kErrCuda;
     }
-    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO>, tmA, tmB, tmC, tmR, tmX8, prm) == cudaSuccess ? kOk : kErrCuda;
+    return cudaLaunchKernelEx(&cfg, gemm_tn_kernel<BN, KIND, PAIR, RES, O8, LNA, LNO, EPI>, tmA, tmB, tmC, tmR, tmX8, prm) == cudaSuccess ? kOk : kErrCuda;
   } else {
     const int grid = tiles < num_sms ? tiles : num_sms;
     gemm_tn_kernel<BN, KIND, 0, 0, 0, 0><<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, tmX8, prm);
@@ -217,7 +217,18 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
   // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&
       (a.p.col_scale == nullptr || KIND == kKindI8)) {
-    if (a.p.out_dtype == kOutE4M3) return gemm_launch_t<256, KIND, 1, 0, 1>(a, num_sms, stream);
+    if (a.p.out_dtype == kOutE4M3) {
+      if constexpr (KIND == kKindF8) {
+        // the three hot shapes of the FP8 engine get epilogues with their switches fixed at compile time
+        const bool plain = a.p.residual == nullptr && a.p.col_scale == nullptr && a.p.N % 64 == 0 &&
+                           (reinterpret_cast<uintptr_t>(a.p.bias) & 15) == 0;
+        if (plain && a.p.act == kActNone && a.p.bias != nullptr) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 1>(a, num_sms, stream);
+        if (plain && a.p.act == kActNone && a.p.bias == nullptr) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 2>(a, num_sms, stream);
+        if (plain && a.p.act == kActMish && a.p.bias != nullptr && a.p.precise_act == 0)
+          return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 3>(a, num_sms, stream);
+      }
+      return gemm_launch_t<256, KIND, 1, 0, 1>(a, num_sms, stream);
+    }
     // a residual that a tensor map can describe is fetched by TMA (out-projection, ff2)
     const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
