@@ -324,9 +324,10 @@ __device__ __forceinline__ bool ln_wait_blocks(uint32_t words_smem, uint32_t blo
   }
 }
 
-// EPI != 0 (CTA pairs with an e4m3 output, no residual, no column scales, N a multiple of 64): the epilogue's switches
-// are fixed at compile time - 1: bias, no activation; 2: no bias, no activation; 3: bias and Mish on packed f16 pairs -
-// which takes their tests and the untaken paths out of the three hottest instantiations. Same arithmetic as EPI = 0.
+// EPI != 0 (CTA pairs; N a multiple of 64, 16-byte aligned tables; a residual only by TMA; int8 operands with per-token
+// and per-channel scales, the others with neither): the epilogue's switches are fixed at compile time - 1: bias, no
+// activation; 2: no bias, no activation; 3: bias and Mish (on packed f16 pairs where the output is e4m3) - which
+// takes their tests and the untaken paths out of the hot instantiations. Same arithmetic as EPI = 0.
 template <int BN, int KIND, int PAIR, int RES, int O8, int LNA, int LNO = 0, int EPI = 0>
 __global__ void __launch_bounds__(kGemmThreads + (LNA ? 32 * kLnWarps : 0), 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -536,6 +537,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // (The shared-memory loads and stores below are volatile asm without a memory clobber: they keep their order among
       // themselves and with every barrier, fence and TMA operation - all volatile asm too - while the read-only
       // parameter loads around them stay free to be scheduled early.)
+      // EPI != 0 fixes the switches at compile time (f16 / e4m3 operands): 1 = bias and an e4m3 copy, 2 = bias, no copy
+      constexpr bool kSpecL = EPI != 0 && KIND != kKindI8;
+      const bool l_bias = kSpecL ? true : (p.bias != nullptr);
+      const bool l_copy = kSpecL ? (EPI == 1) : (p.lno_x8 != nullptr);
       const int set = ew >> 3;
       const int half = (ew >> 2) & 1;          // columns [128 half, +128) of the CTA's 256
       const uint32_t slab = base + Cfg::EPI_OFF + Cfg::TAB_BYTES + ew * Cfg::SLOT_BYTES;     // two 32 x 64 sub-slabs
@@ -667,13 +672,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = static_cast<float>(static_cast<int>(acc[c * 8 + j])) * sc[j];
-              if (p.bias != nullptr) {
+              if (l_bias) {
                 const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
                 const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
                 v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
                 v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
               }
-            } else if (p.bias != nullptr) {
+            } else if (l_bias) {
               const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8));
               const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + c0 + k * 8 + 4));
               const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
@@ -741,7 +746,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (KIND == kKindI8) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(y2[j]));
-          } else {
+          } else if (l_copy) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               const __half2 a = __hmul2(y2[2 * j], s8), b = __hmul2(y2[2 * j + 1], s8);
@@ -789,7 +794,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
         }
-        if (p.lno_x8 != nullptr) {
+        if (l_copy) {
           // the e4m3 copy leaves the same way: once the stores above have read the slab, its first 4 KB take the 32
           // rows of 128 bytes (the same 128-byte swizzle), and one more TMA store follows
           if (lane == 0) bulk_wait_read0();
@@ -843,13 +848,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int rm, rn;
         return tile_of(i, rm, rn) && rn * BN + part * 64 < p.N;
       };
-      const bool tma_res = RES != 0 && p.use_tma_res != 0 && p.residual != nullptr;
+      const bool tma_res = (EPI != 0) ? (RES != 0) : (RES != 0 && p.use_tma_res != 0 && p.residual != nullptr);
       if (RES != 0 && tma_res && res_wanted(0)) res_issue(0);
       constexpr bool kSpec = EPI != 0;
-      static_assert(!kSpec || (O8 != 0 && RES == 0 && KIND != kKindI8), "specialised epilogues: e4m3 output, no residual, no column scales");
+      static_assert(!kSpec || !LNA, "specialised epilogues: not for the kernels with a LayerNorm in front");
       const bool has_bias = kSpec ? (EPI != 2) : (p.bias != nullptr);
       const int act = kSpec ? (EPI == 3 ? kActMish : kActNone) : p.act;
-      const bool mish8 = kSpec ? (EPI == 3) : (O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0);
+      const bool mish8 = kSpec ? (EPI == 3 && O8 != 0) : (O8 != 0 && p.act == kActMish && p.residual == nullptr && p.precise_act == 0);
       if constexpr (LNA) {
         // the worker's first row block: nothing to drain yet, so the epilogue warps normalise rows too
         if (worker < tiles_m) {
@@ -895,10 +900,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int row = m0 + quarter * 32 + lane;
         const bool row_ok = row < p.M;
         const int rrow = p.res_mod > 0 ? row % p.res_mod : row;
-        const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+        // (specialised epilogues: int8 operands come with per-token and per-channel scales, the others with neither)
+        const float rs = kSpec ? ((KIND == kKindI8 && row_ok) ? p.row_scale[row] : 1.0f)
+                               : ((p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f);
         // e4m3 output without an activation or residual: out = (alpha acc + bias) s = (alpha s) acc + (bias s), one
         // multiply-add per element instead of three operations
-        const bool fold = kSpec ? (EPI != 3) : (O8 != 0 && p.act == kActNone && p.residual == nullptr);
+        const bool fold = kSpec ? (O8 != 0 && EPI != 3) : (O8 != 0 && p.act == kActNone && p.residual == nullptr);
         const float os = fold ? 1.0f : p.out_scale;
         const float bs = fold ? p.out_scale : 1.0f;
         const float a_scale = p.alpha * rs * bs;
@@ -948,7 +955,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             sc[j] = a_scale;
           }
           if constexpr (KIND == kKindI8) {
-            if (p.col_scale != nullptr) {
+            if (kSpec || p.col_scale != nullptr) {
               if (tab_vec) {
                 const float4* c4p = reinterpret_cast<const float4*>(p.col_scale + c0 + i * 16);
 #pragma unroll

@@ -212,27 +212,49 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         (reinterpret_cast<uintptr_t>(a.p.bias) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
       return kErrUnsupported;
+    if constexpr (KIND != kKindI8) {
+      // the two forms the engines launch get their switches fixed at compile time
+      if (a.p.bias != nullptr && a.p.lno_x8 != nullptr) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1, 1>(a, num_sms, stream);
+      if (a.p.bias != nullptr && a.p.lno_x8 == nullptr) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1, 2>(a, num_sms, stream);
+    }
     return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);
   }
   // large problems with a 16-bit or 8-bit output a tensor map can describe: CTA pairs on 256 x 256 tiles
   if (a.p.N >= 256 && ((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) >= num_sms / 2 && out_map_ok(a.p) &&
       (a.p.col_scale == nullptr || KIND == kKindI8)) {
-    if (a.p.out_dtype == kOutE4M3) {
-      if constexpr (KIND == kKindF8) {
-        // the three hot shapes of the FP8 engine get epilogues with their switches fixed at compile time
-        const bool plain = a.p.residual == nullptr && a.p.col_scale == nullptr && a.p.N % 64 == 0 &&
-                           (reinterpret_cast<uintptr_t>(a.p.bias) & 15) == 0;
-        if (plain && a.p.act == kActNone && a.p.bias != nullptr) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 1>(a, num_sms, stream);
-        if (plain && a.p.act == kActNone && a.p.bias == nullptr) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 2>(a, num_sms, stream);
-        if (plain && a.p.act == kActMish && a.p.bias != nullptr && a.p.precise_act == 0)
-          return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 3>(a, num_sms, stream);
-      }
-      return gemm_launch_t<256, KIND, 1, 0, 1>(a, num_sms, stream);
-    }
     // a residual that a tensor map can describe is fetched by TMA (out-projection, ff2)
     const bool res_tma = a.p.residual != nullptr && a.p.res_mod == 0 && a.p.ldr % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(a.p.residual) & 15) == 0;
-    return res_tma ? gemm_launch_t<256, KIND, 1, 1, 0>(a, num_sms, stream) : gemm_launch_t<256, KIND, 1, 0, 0>(a, num_sms, stream);
+    // The shapes the engines launch get epilogues with their switches fixed at compile time (EPI): bias or not,
+    // no activation or Mish; int8 operands with both scale vectors, the others with neither.
+    const bool scales = KIND == kKindI8 ? (a.p.row_scale != nullptr && a.p.col_scale != nullptr &&
+                                           (reinterpret_cast<uintptr_t>(a.p.col_scale) & 15) == 0)
+                                        : (a.p.row_scale == nullptr && a.p.col_scale == nullptr);
+    const bool plain = scales && a.p.N % 64 == 0 && (reinterpret_cast<uintptr_t>(a.p.bias) & 15) == 0 &&
+                       (a.p.residual == nullptr || res_tma);
+    int epi = 0;
+    if (plain && a.p.act == kActNone) epi = a.p.bias != nullptr ? 1 : 2;
+    else if (plain && a.p.act == kActMish && a.p.bias != nullptr && a.p.residual == nullptr &&
+             (a.p.out_dtype != kOutE4M3 || a.p.precise_act == 0))
+      epi = 3;
+    if (a.p.out_dtype == kOutE4M3) {
+      if (a.p.residual != nullptr) epi = 0;      // (no hot GEMM adds a residual into an e4m3 output)
+      if constexpr (KIND != kKindI8) {
+        if (epi == 1) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 1>(a, num_sms, stream);
+        if (epi == 2) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 2>(a, num_sms, stream);
+        if (epi == 3) return gemm_launch_t<256, KIND, 1, 0, 1, 0, 0, 3>(a, num_sms, stream);
+      }
+      return gemm_launch_t<256, KIND, 1, 0, 1>(a, num_sms, stream);
+    }
+    if (res_tma) {
+      if (epi == 1) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 0, 1>(a, num_sms, stream);
+      return gemm_launch_t<256, KIND, 1, 1, 0>(a, num_sms, stream);
+    }
+    if (a.p.residual == nullptr) {
+      if (epi == 1) return gemm_launch_t<256, KIND, 1, 0, 0, 0, 0, 1>(a, num_sms, stream);
+      if (epi == 3) return gemm_launch_t<256, KIND, 1, 0, 0, 0, 0, 3>(a, num_sms, stream);
+    }
+    return gemm_launch_t<256, KIND, 1, 0, 0>(a, num_sms, stream);
   }
   if (bn == 64) return gemm_launch_t<64, KIND>(a, num_sms, stream);
   if (bn == 128) return gemm_launch_t<128, KIND>(a, num_sms, stream);
