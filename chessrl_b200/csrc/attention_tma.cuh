@@ -34,7 +34,9 @@ struct AttnTmaSmem {
   static constexpr int BYTES = BAR_OFF + NW * 8 + 1024;
 };
 
-template <int NW>
+// BIAS (0 none, 1 f16 tile, 2 e4m3 tile) and OUT8 (context as e4m3) are fixed at compile time: their tests sit
+// inside the unrolled loops
+template <int NW, int BIAS, int OUT8>
 __global__ void __launch_bounds__(NW * 32, 1)
 attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmBias,
                      const __grid_constant__ CUtensorMap tmOut, const AttnTmaParams p) {
@@ -59,7 +61,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
   const long long items = (long long)p.B * p.H;
   const long long first = (long long)blockIdx.x * NW + warp;
   const long long stride = (long long)gridDim.x * NW;
-  const uint32_t stage_bytes = 3u * 4096u + (p.has_bias == 1 ? 8192u : (p.has_bias == 2 ? 4096u : 0u));
+  const uint32_t stage_bytes = 3u * 4096u + (BIAS == 1 ? 8192u : (BIAS == 2 ? 4096u : 0u));
   const int g = lane >> 2, t = lane & 3;
   const uint32_t k_scale = pack_h2(p.scale * 1.4426950408889634f, p.scale * 1.4426950408889634f);
   const uint32_t k_bias = pack_h2(p.bias_mult * 1.4426950408889634f, p.bias_mult * 1.4426950408889634f);
@@ -72,7 +74,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       tma_load_2d(sQ, &tmQKV, h * 32, board * 64, bar);
       tma_load_2d(sK, &tmQKV, p.d + h * 32, board * 64, bar);
       tma_load_2d(sV, &tmQKV, 2 * p.d + h * 32, board * 64, bar);
-      if (p.has_bias) tma_load_2d(wbase + 12288, &tmBias, 0, static_cast<int>(item * 64), bar);
+      if (BIAS) tma_load_2d(wbase + 12288, &tmBias, 0, static_cast<int>(item * 64), bar);
     }
     if (!mbar_wait(bar, it & 1)) {
       if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue + 10);
@@ -117,7 +119,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       for (int u = 0; u < 2; ++u) {
         const int r0 = (half * 2 + u) * 16 + g;
         // s2 = score * (scale * log2 e) + bias * (bias_mult * log2 e)
-        if (p.has_bias == 1) {
+        if (BIAS == 1) {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
             const uint32_t ba = *reinterpret_cast<const uint32_t*>(sB + r0 * 128 + ((n ^ (r0 & 7)) << 4) + 4 * t);
@@ -125,7 +127,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
             sh[u][n][0] = hfma2_u32(sh[u][n][0], k_scale, hmul2_u32(ba, k_bias));
             sh[u][n][1] = hfma2_u32(sh[u][n][1], k_scale, hmul2_u32(bb, k_bias));
           }
-        } else if (p.has_bias == 2) {
+        } else if (BIAS == 2) {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
             const int ra = r0, rb = r0 + 8;
@@ -184,7 +186,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       for (int u = 0; u < 2; ++u) {
         const int r0 = (half * 2 + u) * 16 + g;
         float inv0 = inv[u][0], inv1 = inv[u][1];
-        if (p.out_e4m3) {
+        if (OUT8) {
           inv0 *= p.out_scale; inv1 *= p.out_scale;
 #pragma unroll
           for (int n = 0; n < 4; ++n) {
@@ -255,7 +257,8 @@ __device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
 // 16-byte piece c (0/1) of row r in a 64 x 32-byte tile written with the 32-byte swizzle
 __device__ __forceinline__ uint32_t tile8_off(int r, int c) { return r * 32 + ((c ^ ((r >> 2) & 1)) << 4); }
 
-template <int NW>
+// BIAS: the smolgen tile is present (fixed at compile time: its test sits inside the unrolled score loops)
+template <int NW, int BIAS>
 __global__ void __launch_bounds__(NW * 32, 1)
 attention_tma8_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmBias,
                       const __grid_constant__ CUtensorMap tmOut, const AttnTma8Params p) {
@@ -280,7 +283,7 @@ attention_tma8_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
   const long long items = (long long)p.B * p.H;
   const long long first = (long long)blockIdx.x * NW + warp;
   const long long stride = (long long)gridDim.x * NW;
-  const uint32_t stage_bytes = 3u * 2048u + (p.has_bias ? 4096u : 0u);
+  const uint32_t stage_bytes = 3u * 2048u + (BIAS ? 4096u : 0u);
   const int g = lane >> 2, t = lane & 3;
   const uint32_t k_scale = pack_h2(p.scale * 1.4426950408889634f, p.scale * 1.4426950408889634f);
   const uint32_t k_bias = pack_h2(p.bias_mult * 1.4426950408889634f, p.bias_mult * 1.4426950408889634f);
@@ -294,7 +297,7 @@ attention_tma8_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
       tma_load_2d(sQ, &tmQKV, h * 32, board * 64, bar);
       tma_load_2d(sK, &tmQKV, p.d + h * 32, board * 64, bar);
       tma_load_2d(sV, &tmQKV, 2 * p.d + h * 32, board * 64, bar);
-      if (p.has_bias) tma_load_2d(wbase + 6144, &tmBias, 0, static_cast<int>(item * 64), bar);
+      if (BIAS) tma_load_2d(wbase + 6144, &tmBias, 0, static_cast<int>(item * 64), bar);
     }
     if (!mbar_wait(bar, it & 1)) {
       if (lane == 0) atomicCAS(p.status, 0, kDevTimeoutEpilogue + 10);
@@ -343,7 +346,7 @@ attention_tma8_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_co
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int r0 = (half * 2 + u) * 16 + g;
-        if (p.has_bias) {
+        if (BIAS) {
 #pragma unroll
           for (int n = 0; n < 8; ++n) {
             const int ra = r0, rb = r0 + 8;

@@ -431,18 +431,18 @@ int tap_mean(crl_handle* h, const __half* x, long long rows, int cols, long long
   return CRL_OK;
 }
 
-template <int NW>
+template <int NW, int BIAS, int OUT8>
 int attention_tma_launch_t(crl_handle* h, const AttnTmaParams& t, const CUtensorMap& tq, const CUtensorMap& tb,
                            const CUtensorMap& to, cudaStream_t s) {
   static bool attr_set[64] = {};
   if (h->device >= 0 && h->device < 64 && !attr_set[h->device]) {
-    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTmaSmem<NW>::BYTES));
+    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma_kernel<NW, BIAS, OUT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTmaSmem<NW>::BYTES));
     attr_set[h->device] = true;
   }
   const long long items = static_cast<long long>(t.B) * t.H;
   const long long want = (items + NW - 1) / NW;
   const unsigned grid = static_cast<unsigned>(want < h->num_sms ? want : h->num_sms);
-  attention_tma_kernel<NW><<<grid, NW * 32, AttnTmaSmem<NW>::BYTES, s>>>(tq, tb, to, t);
+  attention_tma_kernel<NW, BIAS, OUT8><<<grid, NW * 32, AttnTmaSmem<NW>::BYTES, s>>>(tq, tb, to, t);
   CRL_CUDA(h, cudaGetLastError());
   return CRL_OK;
 }
@@ -457,21 +457,25 @@ int attention_tma_launch(crl_handle* h, const AttnTmaParams& t, const __half* qk
   if (rc == kOk && t.has_bias == 2) rc = make_tmap_2d(&tb, bias, 1, 64, static_cast<uint64_t>(t.B) * t.H * 64, 64, 64, 64);
   if (rc == kOk) rc = t.out_e4m3 ? make_tmap_2d(&to, out, 1, t.d, M, t.d, 64, 32) : make_tmap_2d(&to, out, 2, t.d, M, 2ull * t.d, 64, 64);
   if (rc != kOk) return fail(h, rc, "attention: tensor map encoding failed");
-  return t.has_bias == 1 ? attention_tma_launch_t<11>(h, t, tq, tb, to, s) : attention_tma_launch_t<14>(h, t, tq, tb, to, s);
+  if (t.has_bias == 1)
+    return t.out_e4m3 ? attention_tma_launch_t<11, 1, 1>(h, t, tq, tb, to, s) : attention_tma_launch_t<11, 1, 0>(h, t, tq, tb, to, s);
+  if (t.has_bias == 2)
+    return t.out_e4m3 ? attention_tma_launch_t<14, 2, 1>(h, t, tq, tb, to, s) : attention_tma_launch_t<14, 2, 0>(h, t, tq, tb, to, s);
+  return t.out_e4m3 ? attention_tma_launch_t<14, 0, 1>(h, t, tq, tb, to, s) : attention_tma_launch_t<14, 0, 0>(h, t, tq, tb, to, s);
 }
 
-template <int NW>
+template <int NW, int BIAS>
 int attention_tma8_launch_t(crl_handle* h, const AttnTma8Params& t, const CUtensorMap& tq, const CUtensorMap& tb,
                             const CUtensorMap& to, cudaStream_t s) {
   static bool attr_set[64] = {};
   if (h->device >= 0 && h->device < 64 && !attr_set[h->device]) {
-    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma8_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTma8Smem<NW>::BYTES));
+    CRL_CUDA(h, cudaFuncSetAttribute(attention_tma8_kernel<NW, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnTma8Smem<NW>::BYTES));
     attr_set[h->device] = true;
   }
   const long long items = static_cast<long long>(t.B) * t.H;
   const long long want = (items + NW - 1) / NW;
   const unsigned grid = static_cast<unsigned>(want < h->num_sms ? want : h->num_sms);
-  attention_tma8_kernel<NW><<<grid, NW * 32, AttnTma8Smem<NW>::BYTES, s>>>(tq, tb, to, t);
+  attention_tma8_kernel<NW, BIAS><<<grid, NW * 32, AttnTma8Smem<NW>::BYTES, s>>>(tq, tb, to, t);
   CRL_CUDA(h, cudaGetLastError());
   return CRL_OK;
 }
@@ -485,7 +489,7 @@ int attention_tma8_launch(crl_handle* h, const AttnTma8Params& t, const uint8_t*
   if (rc == kOk && t.has_bias == 2) rc = make_tmap_2d(&tb, bias, 1, 64, static_cast<uint64_t>(t.B) * t.H * 64, 64, 64, 64);
   if (rc == kOk) rc = make_tmap_2d(&to, out, 1, t.d, M, t.d, 64, 32);
   if (rc != kOk) return fail(h, rc, "attention: tensor map encoding failed");
-  return attention_tma8_launch_t<16>(h, t, tq, tb, to, s);
+  return t.has_bias != 0 ? attention_tma8_launch_t<16, 1>(h, t, tq, tb, to, s) : attention_tma8_launch_t<16, 0>(h, t, tq, tb, to, s);
 }
 
 int act_of(const crl_config& c) { return c.act == CRL_ACT_MISH ? kActMish : kActGelu; }
