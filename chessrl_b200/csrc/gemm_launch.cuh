@@ -212,8 +212,10 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         (reinterpret_cast<uintptr_t>(a.p.bias) & 15) != 0 ||
         (reinterpret_cast<uintptr_t>(a.p.lno_b16) & 15) != 0 || (reinterpret_cast<uintptr_t>(a.p.lno_stats) & 7) != 0)
       return kErrUnsupported;
+    static const bool generic_only = std::getenv("CRL_GEMM_GENERIC") != nullptr;
     if constexpr (KIND != kKindI8) {
       // the two forms the engines launch get their switches fixed at compile time
+      if (generic_only) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1>(a, num_sms, stream);
       if (a.p.bias != nullptr && a.p.lno_x8 != nullptr) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1, 1>(a, num_sms, stream);
       if (a.p.bias != nullptr && a.p.lno_x8 == nullptr) return gemm_launch_t<256, KIND, 1, 1, 0, 0, 1, 2>(a, num_sms, stream);
     }
@@ -232,8 +234,12 @@ inline int gemm_launch_k(const GemmArgs& a, int num_sms, cudaStream_t stream) {
                                         : (a.p.row_scale == nullptr && a.p.col_scale == nullptr);
     const bool plain = scales && a.p.N % 64 == 0 && (reinterpret_cast<uintptr_t>(a.p.bias) & 15) == 0 &&
                        (a.p.residual == nullptr || res_tma);
+    // (CRL_GEMM_GENERIC in the environment keeps every launch on the run-time switches: the reference the
+    // specialised instantiations are tested against)
+    static const bool generic_only = std::getenv("CRL_GEMM_GENERIC") != nullptr;
     int epi = 0;
-    if (plain && a.p.act == kActNone) epi = a.p.bias != nullptr ? 1 : 2;
+    if (generic_only) epi = 0;
+    else if (plain && a.p.act == kActNone) epi = a.p.bias != nullptr ? 1 : 2;
     else if (plain && a.p.act == kActMish && a.p.bias != nullptr && a.p.residual == nullptr &&
              (a.p.out_dtype != kOutE4M3 || a.p.precise_act == 0))
       epi = 3;

@@ -442,3 +442,83 @@ def test_output_layernorm_is_refused_where_it_cannot_run(lib):
         assert lib.crl_linear_ex(ctypes.byref(x)) == -8, (kind, m, n)
         torch.cuda.synchronize()
         assert bool((c == 3.0).all())
+
+
+_AB_SCRIPT = r'''
+import ctypes, hashlib, sys, torch
+sys.path.insert(0, %(root)r)
+from chessrl_b200 import _lib as L
+lib = L.load()
+torch.manual_seed(1)
+sms = torch.cuda.get_device_properties(0).multi_processor_count
+m = 256 * (sms // 2 + 3) + 64
+h = hashlib.sha256()
+
+def run(kind, n, k, out, bias=True, act=0, res=False, scales=False, lno=False, copy=False):
+    if kind == 1:
+        a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn); w = torch.randn(n, k, device="cuda").to(torch.float8_e4m3fn)
+    elif kind == 2:
+        a = torch.randint(-127, 128, (m, k), device="cuda", dtype=torch.int8); w = torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8)
+    else:
+        a = torch.randn(m, k, device="cuda").half(); w = (torch.randn(n, k, device="cuda") * 0.05).half()
+    c = torch.zeros(m, n, device="cuda", dtype=torch.uint8 if out == 2 else torch.float16)
+    b = torch.randn(n, device="cuda")
+    r = torch.randn(m, n, device="cuda").half()
+    rs = torch.rand(m, device="cuda") * 0.01 + 0.001; cs = torch.rand(n, device="cuda") * 0.01 + 0.001
+    g = (1.0 + 0.1 * torch.randn(n, device="cuda")).half(); be = (0.1 * torch.randn(n, device="cuda")).half()
+    x8 = torch.zeros(m, n, device="cuda", dtype=torch.uint8)
+    scratch = torch.zeros(4096 * ((m + 255) // 256), device="cuda", dtype=torch.int64)
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    x = L.LinearArgs()
+    x.kind, x.out_dtype = kind, out
+    x.a, x.lda, x.w, x.ldw, x.c, x.ldc = a.data_ptr(), k, w.data_ptr(), k, c.data_ptr(), n
+    x.m, x.n, x.k = m, n, k
+    x.bias = b.data_ptr() if bias else None
+    if res or lno:
+        x.residual, x.ldr = r.data_ptr(), n
+    x.alpha, x.act, x.out_scale = (1.0 / 64.0 if kind == 1 else 1.0), act, 3.0
+    if scales:
+        x.row_scale, x.col_scale = rs.data_ptr(), cs.data_ptr()
+    x.device_status = st.data_ptr()
+    if lno:
+        x.lno_weight, x.lno_bias, x.lno_scratch = g.data_ptr(), be.data_ptr(), scratch.data_ptr()
+        if copy:
+            x.lno_x8, x.lno_out8_scale = x8.data_ptr(), 50.0
+    rc = lib.crl_linear_ex(ctypes.byref(x))
+    torch.cuda.synchronize()
+    assert rc == 0 and int(st[0]) == 0, (rc, int(st[0]))
+    h.update(c.cpu().numpy().tobytes()); h.update(x8.cpu().numpy().tobytes())
+
+run(1, 3072, 1024, 2)                       # e4m3 out, bias
+run(1, 4096, 256, 2, bias=False)            # e4m3 out, no bias
+run(1, 1536, 1024, 2, act=2)                # e4m3 out, bias + Mish on packed pairs
+run(1, 1024, 1536, 0, res=True)             # f16 out, residual by TMA
+run(0, 3072, 1024, 0)                       # f16 operands
+run(0, 1536, 1024, 0, act=2)                # f16 operands, Mish in fp32
+run(2, 3072, 1024, 0, scales=True)          # int8 operands with both scale vectors
+run(2, 1024, 1024, 0, scales=True, res=True)
+run(1, 1024, 1024, 0, lno=True, copy=True)  # output LayerNorm with the e4m3 copy
+run(0, 1024, 1024, 0, lno=True)             # ... without
+print(h.hexdigest())
+'''
+
+
+def test_specialised_epilogues_equal_the_generic_one():
+    """The instantiations with compile-time epilogue switches against the generic epilogue (CRL_GEMM_GENERIC keeps every
+    launch on it; the library reads the variable once, hence two processes): every output byte of ten launches that
+    cover each specialised kernel family must agree."""
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    script = _AB_SCRIPT % {"root": ROOT}
+    digests = []
+    for generic in (False, True):
+        env = dict(os.environ)
+        env.pop("CRL_GEMM_GENERIC", None)
+        if generic:
+            env["CRL_GEMM_GENERIC"] = "1"
+        out = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+        digests.append(out.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1]
