@@ -387,7 +387,10 @@ int layer_norm(crl_handle* h, const __half* x, long long rows, int d, const floa
   if (gate_ea == nullptr && rows >= 8192 && (h->cfg.precision & CRL_PREC_LN_F32) == 0) {
     const long long want = (rows + 7) / 8;
     const unsigned grid = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 2));
+    // narrow rows (the smolgen generator rows): a quarter of the registers, so four CTAs per SM keep as many bytes in flight
+    const unsigned grid_narrow = static_cast<unsigned>(std::min<long long>(want, static_cast<long long>(h->num_sms) * 4));
     if (yq != nullptr) ln_rows_persistent_kernel<true><<<grid, 256, 0, s>>>(p);
+    else if (d <= 256) ln_rows_persistent_kernel<false, 1><<<grid_narrow, 256, 0, s>>>(p);
     else ln_rows_persistent_kernel<false><<<grid, 256, 0, s>>>(p);
   } else {
     ln_rows_kernel<<<blocks, 256, 0, s>>>(p);

@@ -215,10 +215,10 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const LnParams p) {
 // parameters of their own columns held in registers as f16 pairs. The plain kernel above re-reads weight and
 // bias through L1 for every row (four times the bytes of the row itself), which made L1 throughput, not HBM,
 // its limit; here a row costs one 16-byte load and at most two stores per lane and vector.
-template <bool Q8>      // Q8: also emit per-token int8 rows (the W8A8 engine)
+// NV: 16-byte vectors per lane, rows of up to 256 NV columns (1 for the 256-wide smolgen generator rows, 4 for d_model)
+template <bool Q8, int NV = 4>      // Q8: also emit per-token int8 rows (the W8A8 engine)
 __global__ void __launch_bounds__(256, 2) ln_rows_persistent_kernel(const LnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int NV = 4;
   const long long stride = (long long)gridDim.x * 8;
   long long row = (long long)blockIdx.x * 8 + warp;
   if (row >= p.rows) return;
