@@ -767,3 +767,44 @@ def test_determinism_and_output_guards():
     assert (p1[0] == canary).all() and (p1[-1] == canary).all() and (p1[1:-1, 1858:] == canary).all()
     assert (w1[0] == canary).all() and (w1[-1] == canary).all()
     assert torch.isfinite(p1[1:-1, :1858]).all() and torch.allclose(p1[1:-1, :1858].sum(-1), torch.ones(b), atol=1e-4)
+
+
+def test_cuda_graph_of_a_pass_with_the_layernorm_inside_the_gemms():
+    """A large pass (LayerNorms inside the out-projection / ff2 kernels: a memset of the exchange buffer plus a
+    kernel whose CTAs wait for one another) captured into a CUDA graph replays to the bits of the eager call."""
+    from chessrl_b200 import Engine, EngineConfig, positions
+    import chessrl_b200 as crl
+    cfg = bt4spec.SpecConfig.baseline(2, 512, 512, 8, smolgen=True)
+    sd = bt4spec.seeded_state_dict(bt4spec.BT4Spec(cfg), seed=29)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    b = 4 * sms + 37
+    pos = positions.playout_positions(b, seed=31)
+    planes, bits = pos["planes112"].cuda(), pos["legal1858"].cuda()
+    eng = Engine(EngineConfig(dtype=crl.DTYPE_F8E4M3, **cfg.to_dict()))
+    eng.load_state_dict(sd)
+    eng.calibrate(planes[:256])
+
+    def call():
+        return eng.forward(planes, legal_mask=bits)
+
+    eager = call()
+    torch.cuda.synchronize()
+    want = {k: v.clone() for k, v in eager.items()}
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = call()
+    for _ in range(3):
+        for v in out.values():
+            v.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        rc, st = eng.last_status()
+        assert rc == 0 and st == 0
+        for k in want:
+            assert torch.equal(out[k], want[k]), k
+    eng.close()
